@@ -1,0 +1,385 @@
+"""Benchmark of the AWQ W4A16 linear path on B200.
+
+Workload ("w4a16_gemm_sweep"): the 30-point GEMM shape sweep at group size 128,
+M in {1, 4, 16, 128, 1024, 4096} x (K, N) in {(4096,4096), (4096,12288),
+(12288,4096), (5120,25600), (25600,5120)}, fp16, seeded synthetic inputs with
+the benchmark's distributions (int4 weights and zero-points uniform in [0,15],
+scales uniform in [1e-3,1e-2], activations N(0,1)).  One step is one pass over
+all 30 points; the metric is the time of that pass in microseconds (lower is
+better).  Weights rotate over enough distinct copies per shape that a call
+never finds its weights in L2.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+With --gpus N > 1 (launched by torch.distributed.run) the same sweep runs
+tensor-parallel: column-parallel shards along N, row-parallel shards along K on
+group boundaries followed by an NCCL all-reduce (strong scaling).
+
+--impl reference times the CPU restatement of the reference arithmetic (unpack
+by shifts, (q - z) * s, fp32 matmul) on the host cores, on a bounded sample of
+the sweep.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+MS = (1, 4, 16, 128, 1024, 4096)
+# (K, N, how the layer is sharded under tensor parallelism)
+SHAPES = ((4096, 4096, "column"), (4096, 12288, "column"), (12288, 4096, "row"),
+          (5120, 25600, "column"), (25600, 5120, "row"))
+GROUP = 128
+L2_BYTES = 126 * 1024 * 1024
+
+
+def weight_bytes(K, N, g=GROUP):
+    return K * N // 2 + 2 * (K // g) * N + 4 * (K // g) * (N // 8)
+
+
+def algo_bytes(M, K, N, g=GROUP):
+    return weight_bytes(K, N, g) + 2 * M * K + 2 * M * N
+
+
+def algo_flops(M, K, N):
+    return 2 * M * N * K
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"],
+                "tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------
+# clocks sampled during the timed region
+# --------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------
+def shard_shape(K, N, kind, world):
+    if world == 1:
+        return K, N
+    if kind == "column":
+        return K, N // world
+    return K // world, N
+
+
+def make_layer(K, N, seed, dev, dtype):
+    """A WQLinear_GEMM filled on the device with the benchmark's distributions."""
+    import nanoquantization_b200 as nq
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    lin = nq.WQLinear_GEMM(4, GROUP, K, N, dev, False, dtype)
+    # uniform 32-bit words = uniform nibbles, i.e. int4 weights / zero-points uniform in [0, 15]
+    lin.qweight.copy_(torch.randint(-2 ** 31, 2 ** 31, (K, N // 8), generator=g, device=dev, dtype=torch.int64).to(torch.int32))
+    lin.qzeros.copy_(torch.randint(-2 ** 31, 2 ** 31, (K // GROUP, N // 8), generator=g, device=dev, dtype=torch.int64).to(torch.int32))
+    lin.qscales.copy_((torch.rand(K // GROUP, N, generator=g, device=dev) * 9e-3 + 1e-3).to(dtype))
+    return lin
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import nanoquantization_b200 as nq  # noqa: F401
+    from nanoquantization_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = torch.float16
+    lib = _lib.load()
+    assert lib.nqb200_device_supported(local) == 1, "not a B200"
+
+    # layers: enough copies per shape that one pass over the copies exceeds L2
+    layers, xs_dev, xs_host, ys_host = {}, {}, {}, {}
+    for si, (K, N, kind) in enumerate(SHAPES):
+        k, n = shard_shape(K, N, kind, world)
+        ncopy = max(2, -(-int(1.5 * L2_BYTES) // weight_bytes(k, n)))
+        layers[si] = [make_layer(k, n, 1000 * si + c + 17 * rank, dev, dtype) for c in range(ncopy)]
+        for M in MS:
+            g = torch.Generator(device="cpu"); g.manual_seed(M * 31 + si)
+            xh = torch.randn(M, k, generator=g).to(dtype).pin_memory()
+            xs_host[(si, M)] = xh
+            xs_dev[(si, M)] = xh.to(dev)
+            ys_host[(si, M)] = torch.empty(M, n, dtype=dtype).pin_memory()
+    points = [(si, M) for M in MS for si in range(len(SHAPES))]  # M-major: a shape's reuses are far apart
+
+    def call(si, M, step, x):
+        lin = layers[si][step % len(layers[si])]
+        y = lin(x)
+        if world > 1 and SHAPES[si][2] == "row":
+            dist.all_reduce(y)
+        return y
+
+    def sweep_device(step):
+        for (si, M) in points:
+            call(si, M, step, xs_dev[(si, M)])
+
+    def sweep_e2e(step):
+        last = None
+        for (si, M) in points:
+            x = xs_host[(si, M)].to(dev, non_blocking=True)
+            y = call(si, M, step, x)
+            ys_host[(si, M)].copy_(y, non_blocking=True)
+            last = y
+        return last
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, offset):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(steps):
+            fn(offset + s)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for w in range(max(args.warmup, 3)):
+        sweep_device(w)
+        sweep_e2e(w)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_dev = timed(sweep_device, args.steps, 100)
+    ms_e2e = timed(sweep_e2e, args.steps, 200)
+
+    # per-point pass: each point launched back to back over rotating weight copies
+    per_point = []
+    for (si, M) in points:
+        K, N, kind = SHAPES[si]
+        k, n = shard_shape(K, N, kind, world)
+        reps = max(8, 2 * len(layers[si])) if M <= 128 else 4
+        for r in range(3):
+            call(si, M, r, xs_dev[(si, M)])
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for r in range(reps):
+            call(si, M, r, xs_dev[(si, M)])
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        per_point.append({"M": M, "K": k, "N": n, "us": us,
+                          "kernel": lib.nqb200_gemm_kernel_name(M, n, k, GROUP, 0).decode()})
+    clocks = sampler.stop() if rank == 0 else None
+    barrier()
+
+    if rank == 0:
+        pk = peaks()
+        for p in per_point:
+            gbs = algo_bytes(p["M"], p["K"], p["N"]) / p["us"] / 1e3
+            tfl = algo_flops(p["M"], p["K"], p["N"]) / p["us"] / 1e6
+            p.update({"gbs": round(gbs, 1), "tflops": round(tfl, 2), "hbm_frac": round(gbs / pk["hbm_gbs"], 4),
+                      "tensor_frac": round(tfl / pk["tflops_burst"], 4), "us": round(p["us"], 2)})
+
+        def agg(sel, kind):
+            pts = [p for p in per_point if sel(p)]
+            t = sum(p["us"] for p in pts)
+            if kind == "hbm":
+                a = sum(algo_bytes(p["M"], p["K"], p["N"]) for p in pts) / t / 1e3
+                return {"bound": "hbm", "achieved": round(a, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                        "frac": round(a / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                        "kernel": pts[0]["kernel"], "points": len(pts)}
+            a = sum(algo_flops(p["M"], p["K"], p["N"]) for p in pts) / t / 1e6
+            return {"bound": "tensor", "achieved": round(a, 1), "peak": pk["tflops_burst"], "unit": "TFLOP/s",
+                    "frac": round(a / pk["tflops_burst"], 4), "traffic": None, "peak_source": pk["source"],
+                    "kernel": pts[0]["kernel"], "points": len(pts)}
+
+        roof_prefill = agg(lambda p: p["M"] >= 1024, "tensor")   # where the sweep's time goes
+        roof_decode = agg(lambda p: p["M"] <= 16, "hbm")
+        h2d = sum(2 * M * shard_shape(*SHAPES[si], world)[0] for (si, M) in points)
+        d2h = sum(2 * M * shard_shape(*SHAPES[si], world)[1] for (si, M) in points)
+        us_step = ms_dev * 1e3 / args.steps
+        line = {
+            "metric": "w4a16_gemm_sweep_us", "value": round(us_step, 2), "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(us_step / 1e3, 4),
+            "higher_is_better": False, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "w4a16_gemm_sweep g128 M{1,4,16,128,1024,4096} x 5 (K,N) shapes (config 2)",
+                       "points_per_step": len(points), "parallelism": f"tp{world}",
+                       "l2": "weights rotate over copies totalling >1.5x L2 per shape"},
+            "e2e": {"value": round(ms_e2e * 1e3 / args.steps, 2), "unit": "us", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": len(points) * args.steps,
+            "roofline": roof_prefill, "roofline_decode": roof_decode,
+            "clocks": clocks, "points": per_point,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(seconds_budget=20.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------
+# CPU arm: the restatement of the reference arithmetic on the host cores
+# --------------------------------------------------------------------------
+def _cpu_sweep_estimate(shapes, ms_measured, reps=1):
+    """Time unpack+dequant once per shape (it does not depend on M) and the fp32
+    matmul for the measured M; larger M are extrapolated linearly from the
+    largest measured M (a CPU GEMM is already compute-bound there)."""
+    from oracle import awq_oracle as O
+    total_us, detail = 0.0, []
+    for (K, N, _kind) in shapes:
+        c = O.make_case(K, N, 1, seed=K // 128)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            W = O.dequantize(c["qweight"], c["qscales"], c["qzeros"]).float()
+        t_deq = (time.perf_counter() - t0) / reps
+        t_mm = {}
+        for M in ms_measured:
+            x = torch.randn(M, K).to(torch.float16).float()
+            x @ W
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                x @ W
+            t_mm[M] = (time.perf_counter() - t0) / reps
+        mtop = max(ms_measured)
+        for M in MS:
+            mm = t_mm[M] if M in t_mm else t_mm[mtop] * M / mtop
+            total_us += (t_deq + mm) * 1e6
+        detail.append({"K": K, "N": N, "dequant_ms": round(t_deq * 1e3, 2),
+                       "matmul_ms": {str(m): round(v * 1e3, 3) for m, v in t_mm.items()}})
+    return total_us, detail
+
+
+def cpu_baseline(seconds_budget=20.0):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    # bounded sample: the two smallest shapes, measured M in {1, 16, 128}
+    shapes = SHAPES[:2]
+    t0 = time.perf_counter()
+    us, detail = _cpu_sweep_estimate(shapes, (1, 16, 128))
+    frac_of_sweep_flops = sum(K * N for K, N, _ in shapes) / sum(K * N for K, N, _ in SHAPES)
+    return {"value": round(us / frac_of_sweep_flops, 1), "unit": "us", "cores": cores, "kind": "port",
+            "sample": ("CPU restatement (unpack by shifts, (q-z)*s, fp32 matmul; torch, all host threads) on shapes "
+                       "(4096,4096),(4096,12288): dequant once per call, matmul measured at M=1,16,128 and "
+                       "extrapolated linearly in M above 128; scaled to the 5-shape sweep by K*N"),
+            "wall_s": round(time.perf_counter() - t0, 1), "detail": detail}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    steps, warm = args.steps, max(args.warmup, 1)
+    shapes = SHAPES[:2]
+    frac = sum(K * N for K, N, _ in shapes) / sum(K * N for K, N, _ in SHAPES)
+    for _ in range(min(warm, 1)):
+        _cpu_sweep_estimate(shapes[:1], (1,))
+    t0 = time.perf_counter()
+    vals = []
+    for _ in range(min(steps, 3)):
+        us, _d = _cpu_sweep_estimate(shapes, (1, 16, 128))
+        vals.append(us / frac)
+    us = sum(vals) / len(vals)
+    sample = ("CPU restatement of the reference arithmetic (torch, all host threads) on shapes (4096,4096),(4096,12288); "
+              "matmul measured at M=1,16,128, extrapolated linearly in M above 128, scaled to the 5-shape sweep by K*N; "
+              f"{len(vals)} timed samples")
+    line = {"impl": "reference", "metric": "w4a16_gemm_sweep_us", "value": round(us, 1), "unit": "us",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": round(us / 1e3, 3),
+            "higher_is_better": False, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "w4a16_gemm_sweep g128 M{1,4,16,128,1024,4096} x 5 (K,N) shapes (config 2)",
+                       "points_per_step": len(MS) * len(SHAPES), "parallelism": "host cores"},
+            "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": round(time.perf_counter() - t0, 1)}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,89 @@
+/* nqb200 -- C ABI of the B200 (sm_100a) AWQ W4A16 linear kernels.
+ *
+ * Every entry point takes plain device pointers and sizes; nothing here
+ * allocates, frees or retains device memory, throws, aborts or traps.  All
+ * functions returning int return NQB200_OK (0) or a nonzero status; the text
+ * for a status comes from nqb200_status_string().
+ *
+ * Data layout (row-major, contiguous), as written by the reference packer
+ * nanoquantization/layers/gemm.py:447-550:
+ *   qweight  int32 [K, N/8]    nibble j of a word holds column 8*i + {0,2,4,6,1,3,5,7}[j]
+ *   qscales  f16|bf16 [K/g, N]
+ *   qzeros   int32 [K/g, N/8]  packed like qweight
+ *   x        f16|bf16 [M, K]   (same dtype as qscales)
+ *   out      f16|bf16 [M, N]
+ * All pointers must be 16-byte aligned.  `stream` is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).  Calls are asynchronous on it.
+ */
+#ifndef NQB200_H
+#define NQB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  NQB200_OK = 0,
+  NQB200_ERR_BAD_SHAPE = 1,     /* a size is <= 0 or violates K % g, N % 8 */
+  NQB200_ERR_BAD_DTYPE = 2,
+  NQB200_ERR_MISALIGNED = 3,    /* a pointer is not 16-byte aligned */
+  NQB200_ERR_NULL_POINTER = 4,
+  NQB200_ERR_WORKSPACE = 5,     /* workspace missing or too small */
+  NQB200_ERR_UNSUPPORTED_DEVICE = 6, /* not compute capability 10.x */
+  NQB200_ERR_LAUNCH = 7,        /* the CUDA runtime refused the launch */
+  NQB200_ERR_WAIT_TIMEOUT = 8,  /* a bounded device-side wait gave up */
+  NQB200_ERR_TOO_LARGE = 9      /* a size exceeds a stated maximum */
+};
+
+enum { NQB200_F16 = 0, NQB200_BF16 = 1 };
+
+/* Library version (major*100 + minor). */
+int nqb200_version(void);
+
+/* Text for a status code; never NULL. */
+const char* nqb200_status_string(int status);
+
+/* 1 if `device` has compute capability 10.x (B200), 0 otherwise, <0 on a CUDA error. */
+int nqb200_device_supported(int device);
+
+/* Unpack int4 values to natural column order, one byte each (0..15).
+ * out_u8[r, 8*i + e] = (words[r, i] >> {0,16,4,20,8,24,12,28}[e]) & 0xF.
+ * Replaces the shift/mask step of the reference kernels, gemm.py:64-69 and
+ * gemm.py:301-302; serves qweight and qzeros alike.  Bit-exact. */
+int nqb200_unpack_int4(const void* words, void* out_u8, int64_t rows, int64_t cols_packed,
+                       void* stream);
+
+/* Dense weight W[K, N] = dtype(q - z) * s in the scale dtype, one rounding per
+ * element.  Replaces awq_dequantize, gemm.py:126-180 (kernel gemm.py:10-123).
+ * Bit-exact with that arithmetic, including at ragged N where the reference
+ * kernel's load mask is wrong. */
+int nqb200_dequant(const void* qweight, const void* qscales, const void* qzeros, void* out,
+                   int64_t K, int64_t N, int64_t group_size, int dtype, void* stream);
+
+/* Bytes of scratch nqb200_gemm needs for this problem.  The scratch must be
+ * zero-filled once before its first use (the kernels restore it to zero), and
+ * must not be shared by calls that can overlap on the GPU. */
+size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
+
+/* out[M, N] = x[M, K] @ ((q - z) * s) (+ bias), fp32 accumulation, result in
+ * `dtype`.  Replaces both branches of WQLinear_GEMM.forward, gemm.py:552-567:
+ * awq_gemm (gemm.py:329-379, M < 256) and awq_dequantize + torch.matmul
+ * (gemm.py:560-561, M >= 256), and the bias add gemm.py:565-566.
+ * `bias` may be NULL; `bias_dtype` is NQB200_F16 or NQB200_BF16 (the reference
+ * module stores its bias in bf16, gemm.py:435-443). */
+int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                const void* bias, int bias_dtype, void* out,
+                int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Name of the kernel family nqb200_gemm would pick for this problem
+ * ("decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
+const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NQB200_H */

@@ -1,0 +1,72 @@
+// C ABI of the library: argument checks and kernel choice.  No allocation,
+// no exceptions, no global mutable state.
+#include "common.cuh"
+
+using namespace nqb200;
+
+extern "C" int nqb200_version(void) { return 100; }
+
+extern "C" const char* nqb200_status_string(int status) {
+  switch (status) {
+    case NQB200_OK: return "ok";
+    case NQB200_ERR_BAD_SHAPE: return "bad shape: sizes must be positive, K % group_size == 0 and N % 8 == 0";
+    case NQB200_ERR_BAD_DTYPE: return "bad dtype: expected NQB200_F16 or NQB200_BF16";
+    case NQB200_ERR_MISALIGNED: return "misaligned pointer: every buffer must be 16-byte aligned";
+    case NQB200_ERR_NULL_POINTER: return "null pointer";
+    case NQB200_ERR_WORKSPACE: return "workspace missing or smaller than nqb200_gemm_workspace_bytes()";
+    case NQB200_ERR_UNSUPPORTED_DEVICE: return "unsupported device: the kernels are built for sm_100a (B200) only";
+    case NQB200_ERR_LAUNCH: return "CUDA launch failed";
+    case NQB200_ERR_WAIT_TIMEOUT: return "a bounded device-side wait timed out";
+    case NQB200_ERR_TOO_LARGE: return "size exceeds the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int nqb200_device_supported(int device) {
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return major == 10 ? 1 : 0;
+}
+
+static int check_shape(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
+  if (M < 0 || N <= 0 || K <= 0 || g <= 0 || K % g != 0 || N % 8 != 0) return NQB200_ERR_BAD_SHAPE;
+  if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24)) return NQB200_ERR_TOO_LARGE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  return NQB200_OK;
+}
+
+extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
+  if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
+  if (!decode_mma_supports(M, N, K, g)) return 0;
+  const DecodePlan p = plan_decode(M, N, K, g);
+  return p.ksplit > 1 ? p.counter_bytes + p.partial_bytes : 0;
+}
+
+extern "C" const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
+  if (check_shape(M, N, K, g, dtype) != NQB200_OK) return "invalid";
+  if (!decode_mma_supports(M, N, K, g)) return "generic";
+  return "decode_mma";
+}
+
+extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                           const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
+                           int64_t g, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  const int st = check_shape(M, N, K, g, dtype);
+  if (st != NQB200_OK) return st;
+  if (M == 0) return NQB200_OK;
+  if (!x || !qweight || !qscales || !qzeros || !out) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(qscales) || !aligned16(qzeros) || !aligned16(out) ||
+      (bias && !aligned16(bias)))
+    return NQB200_ERR_MISALIGNED;
+  if (bias && bias_dtype != NQB200_F16 && bias_dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  GemmArgs a;
+  a.x = x; a.qw = (const uint32_t*)qweight; a.sc = qscales; a.qz = (const uint32_t*)qzeros;
+  a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
+  if (decode_mma_supports(M, N, K, g)) return launch_decode_mma(a);
+  return launch_generic(a);
+}

@@ -1,0 +1,63 @@
+// Shared helpers for the nqb200 kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "nqb200.h"
+
+namespace nqb200 {
+
+constexpr int kNumSMs = 148;          // B200: 2 dies x 74 SMs
+constexpr int kCounterBytes = 1 << 16; // head of the workspace: tile-arrival counters
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static inline int check_launch() {
+  return cudaGetLastError() == cudaSuccess ? NQB200_OK : NQB200_ERR_LAUNCH;
+}
+
+// How the split-K decode kernel tiles a problem; the same plan sizes the workspace.
+struct DecodePlan {
+  int mt;        // 8-token tiles per CTA (1 or 2)
+  int ng;        // packed words per thread per row (4 -> 256-column CTA tile, 2 -> 128)
+  int tile_n;    // 64 * ng
+  int ntiles;    // ceil(N / tile_n)
+  int mchunks;   // ceil(M / (8*mt))
+  int gpc;       // quantisation groups per CTA
+  int ksplit;    // CTAs along K
+  size_t counter_bytes;
+  size_t partial_bytes;
+};
+DecodePlan plan_decode(int64_t M, int64_t N, int64_t K, int64_t g);
+
+struct GemmArgs {
+  const void* x; const uint32_t* qw; const void* sc; const uint32_t* qz;
+  const void* bias; int bias_dtype; void* out;
+  int M, N, K, g;
+  int dtype;
+  void* ws; size_t ws_bytes;
+  cudaStream_t stream;
+};
+
+int launch_decode_mma(const GemmArgs& a);
+int launch_generic(const GemmArgs& a);
+bool decode_mma_supports(int64_t M, int64_t N, int64_t K, int64_t g);
+
+// ---- device helpers -------------------------------------------------------
+__device__ __forceinline__ float bias_to_float(const void* bias, int bias_dtype, int n) {
+  if (bias_dtype == NQB200_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n]);
+  return __half2float(reinterpret_cast<const __half*>(bias)[n]);
+}
+
+template <bool BF16> __device__ __forceinline__ float raw16_to_float(uint16_t v) {
+  if (BF16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  return __half2float(__ushort_as_half(v));
+}
+template <bool BF16> __device__ __forceinline__ uint16_t float_to_raw16(float f) {
+  if (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+  return __half_as_ushort(__float2half_rn(f));
+}
+
+}  // namespace nqb200

@@ -1,0 +1,49 @@
+"""The C-ABI library loads without a GPU and exports every function the header declares."""
+import ctypes
+import os
+import re
+
+from nanoquantization_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    names = []
+    inc = os.path.join(ROOT, "include")
+    for f in sorted(os.listdir(inc)):
+        if f.endswith(".h"):
+            src = open(os.path.join(inc, f)).read()
+            src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+            names += re.findall(r"\b(nqb200_[a-z0-9_]+)\s*\(", src)
+    return sorted(set(names))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.load()
+    declared = _declared()
+    assert len(declared) >= 8
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == declared
+
+
+def test_host_only_entry_points():
+    lib = _lib.load()
+    assert lib.nqb200_version() >= 100
+    for code in range(0, 12):
+        assert lib.nqb200_status_string(code)
+    # bad arguments are reported as statuses, never as a crash
+    assert lib.nqb200_gemm(None, None, None, None, None, 0, None, 1, 7, 128, 128, 0, None, 0, None) == 1
+    assert lib.nqb200_gemm(None, None, None, None, None, 0, None, 1, 8, 128, 128, 5, None, 0, None) == 2
+    assert lib.nqb200_gemm(None, None, None, None, None, 0, None, 1, 8, 128, 128, 0, None, 0, None) == 4
+    assert lib.nqb200_gemm(None, None, None, None, None, 0, None, 0, 8, 128, 128, 0, None, 0, None) == 0
+    assert lib.nqb200_dequant(None, None, None, None, 100, 8, 64, 0, None) == 1
+    assert lib.nqb200_unpack_int4(None, None, 0, 0, None) == 0
+    buf = ctypes.create_string_buffer(64)
+    mis = ctypes.addressof(buf) | 8
+    assert lib.nqb200_unpack_int4(mis, mis, 1, 1, None) == 3
+    assert lib.nqb200_gemm_workspace_bytes(1, 4096, 4096, 128, 0) > 0
+    assert lib.nqb200_gemm_kernel_name(1, 4096, 4096, 128, 0) in (b"decode_mma",)
+    assert lib.nqb200_gemm_kernel_name(1, 24, 100, 100, 0) == b"generic"

@@ -1,0 +1,213 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and with the
+vectors produced by the reference.  Integer work is bit-exact; the GEMM is
+checked with max|y - y_ref| / max|y_ref| <= 1e-2 (the stated fp16
+accumulation-order tolerance) against fp32 dequantise-then-matmul."""
+import numpy as np
+import pytest
+import torch
+
+import nanoquantization_b200 as nq
+from nanoquantization_b200 import _lib
+from oracle import awq_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2       # the tolerance the path is specified to
+TIGHT = 2e-3     # what a correct kernel achieves here (one 16-bit rounding of the output)
+DEV = "cuda:0"
+
+
+def _tags(npz, suffix):
+    return sorted({k[: -len(suffix)] for k in npz.files if k.endswith(suffix)})
+
+
+def _bits(t):
+    return t.detach().cpu().view(torch.int16).numpy().view(np.uint16)
+
+
+def test_library_is_loaded_and_device_supported():
+    lib = _lib.load()
+    assert lib.nqb200_device_supported(0) == 1
+
+
+# ------------------------------------------------------------------ unpack
+def test_unpack_bit_exact_golden(golden):
+    z = golden("pack_vectors.npz")
+    for t in _tags(z, ".iw"):
+        for words, vals in ((z[t + ".qweight"], z[t + ".iw"]), (z[t + ".qzeros"], z[t + ".iz"])):
+            got = nq.unpack_int4(torch.from_numpy(words).to(DEV)).cpu().numpy()
+            assert np.array_equal(got, vals), t
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (3, 40), (4096, 4096), (200, 25600)])
+def test_unpack_bit_exact_random(rows, cols):
+    rng = np.random.default_rng(rows * 7 + cols)
+    words = rng.integers(0, 2 ** 32, size=(rows, cols // 8), dtype=np.uint64).astype(np.uint32).view(np.int32)
+    got = nq.unpack_int4(torch.from_numpy(words).to(DEV)).cpu().numpy()
+    assert np.array_equal(got, O.unpack_int4(words))
+
+
+def test_unpack_empty():
+    assert nq.unpack_int4(torch.zeros(0, 4, dtype=torch.int32, device=DEV)).shape == (0, 32)
+
+
+# ----------------------------------------------------------------- dequant
+def test_dequant_bit_exact_vs_reference_kernel_vectors(golden):
+    for name in ("from_linear_vectors.npz", "kernel_vectors.npz"):
+        z = golden(name)
+        for t in _tags(z, ".dequant"):
+            W = nq.awq_dequantize(torch.from_numpy(z[t + ".qweight"]).to(DEV), torch.from_numpy(z[t + ".qscales"]).to(DEV),
+                                  torch.from_numpy(z[t + ".qzeros"]).to(DEV))
+            assert W.dtype == torch.float16 and tuple(W.shape) == z[t + ".dequant"].shape
+            assert np.array_equal(_bits(W), z[t + ".dequant"].view(np.uint16)), t
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("K,N,g", [(1024, 3072, 128), (128, 8, 128), (256, 136, 128), (3200, 3200, 128),
+                                   (96, 64, 32), (192, 264, 64), (200, 24, 200)])
+def test_dequant_bit_exact_vs_oracle(dtype, K, N, g):
+    c = O.make_case(K, N, 1, group_size=g, dtype=dtype, seed=K + N)
+    W = nq.awq_dequantize(c["qweight"].to(DEV), c["qscales"].to(DEV), c["qzeros"].to(DEV))
+    ref = O.dequantize(c["qweight"], c["qscales"], c["qzeros"])
+    assert W.dtype == dtype
+    assert np.array_equal(_bits(W), _bits(ref))
+
+
+# -------------------------------------------------------------------- gemm
+def _run_case(K, N, M, g=128, dtype=torch.float16, seed=0, bias=False, tol=TIGHT):
+    c = O.make_case(K, N, M, group_size=g, dtype=dtype, seed=seed, bias=bias)
+    m = nq.WQLinear_GEMM(4, g, K, N, DEV, bias, dtype)
+    m.qweight.copy_(c["qweight"]); m.qscales.copy_(c["qscales"]); m.qzeros.copy_(c["qzeros"])
+    if bias:
+        m.bias.copy_(c["bias"])
+    y = m(c["x"].to(DEV))
+    torch.cuda.synchronize()
+    assert y.dtype == dtype and tuple(y.shape) == (M, N)
+    ref = O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"], c["bias"])
+    err = O.rel_err(y, ref)
+    bound = tol if dtype == torch.float16 else max(tol, 8e-3)  # bf16 output rounding is 2^-8 relative
+    assert err <= bound <= TOL, f"rel err {err:.3e} (K={K} N={N} M={M} g={g} {dtype})"
+    return y, ref
+
+
+def test_gemm_vs_reference_kernel_vectors(golden):
+    for name in ("from_linear_vectors.npz", "kernel_vectors.npz"):
+        z = golden(name)
+        for t in _tags(z, ".gemm"):
+            x = torch.from_numpy(z[t + ".x"])
+            qs = torch.from_numpy(z[t + ".qscales"])
+            y = nq.awq_gemm(x.to(DEV), torch.from_numpy(z[t + ".qweight"]).to(DEV), qs.to(DEV),
+                            torch.from_numpy(z[t + ".qzeros"]).to(DEV), 8)
+            ref32 = O.w4a16_ref(x, z[t + ".qweight"], qs, z[t + ".qzeros"])
+            assert O.rel_err(y, ref32) <= TIGHT, t
+            # and against what the reference's own kernel produced for these inputs
+            assert O.rel_err(y, torch.from_numpy(z[t + ".gemm"])) <= TOL, t
+            assert y.dtype == torch.float16
+
+
+def test_gemm_config1_reference_runnable_case():
+    # Qwen3-0.6B gate_proj: K=1024, N=3072, M=16, fp16
+    _run_case(1024, 3072, 16)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 7, 8, 9, 16, 17, 33, 128])
+def test_gemm_token_counts(M):
+    _run_case(512, 1024, M, seed=M)
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 12288), (12288, 4096), (5120, 25600), (25600, 5120)])
+@pytest.mark.parametrize("M", [1, 16])
+def test_gemm_sweep_shapes_decode(K, N, M):
+    _run_case(K, N, M, seed=K // 128 + M)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("K,N,g,M", [
+    (128, 128, 128, 1),       # one group, one k/v head per rank at TP=8
+    (512, 128, 128, 3),
+    (3200, 5120, 128, 5),     # 25 groups: Qwen3-32B down_proj shard at TP=8
+    (5120, 3200, 128, 16),    # N = 3200, not a multiple of 256
+    (256, 144, 128, 4),       # N % 32 != 0 -> 64-bit loads
+    (256, 136, 128, 2),       # N % 16 != 0 -> fallback kernel
+    (96, 64, 32, 8),
+    (192, 256, 64, 12),
+    (1024, 2048, 32, 8),      # the reference unit test's shape
+    (200, 24, 200, 3),        # group == K, not a multiple of 16 -> fallback kernel
+    (4096, 64, 4096, 2),      # group == K
+])
+def test_gemm_edge_shapes(dtype, K, N, g, M):
+    _run_case(K, N, M, g=g, dtype=dtype, seed=K + N + M)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [1, 16, 40])
+def test_gemm_bias(dtype, M):
+    _run_case(1024, 512, M, dtype=dtype, bias=True, seed=9)
+
+
+def test_gemm_leading_dims_and_empty():
+    c = O.make_case(256, 128, 6, seed=4)
+    m = nq.WQLinear_GEMM(4, 128, 256, 128, DEV, False, torch.float16)
+    m.qweight.copy_(c["qweight"]); m.qscales.copy_(c["qscales"]); m.qzeros.copy_(c["qzeros"])
+    y = m(c["x"].to(DEV).view(2, 3, 256))
+    assert tuple(y.shape) == (2, 3, 128)
+    assert O.rel_err(y.view(6, 128), O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"])) <= TIGHT
+    assert tuple(m(torch.zeros(0, 256, dtype=torch.float16, device=DEV)).shape) == (0, 128)
+
+
+def test_gemm_is_deterministic_and_restores_workspace():
+    c = O.make_case(4096, 4096, 4, seed=21)
+    args = [c["x"].to(DEV), c["qweight"].to(DEV), c["qscales"].to(DEV), c["qzeros"].to(DEV), 8]
+    y1 = nq.awq_gemm(*args)
+    y2 = nq.awq_gemm(*args)
+    y3 = nq.awq_gemm(*args)
+    assert torch.equal(y1, y2) and torch.equal(y1, y3)
+    for ws in _lib._workspaces.values():
+        assert int(ws[: 1 << 16].view(torch.int32).abs().sum()) == 0  # arrival counters back at zero
+
+
+def test_gemm_x_is_cast_to_output_dtype():
+    c = O.make_case(256, 128, 3, seed=2)
+    y = nq.awq_gemm(c["x"].float().to(DEV), c["qweight"].to(DEV), c["qscales"].to(DEV), c["qzeros"].to(DEV), 8)
+    assert y.dtype == torch.float16
+    assert O.rel_err(y, O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"])) <= TIGHT
+
+
+def test_gemm_outlier_activations_and_extreme_nibbles():
+    # large-mean activations stress the zero-point / sum(x) correction; all-15 weights with all-0
+    # zero-points and the reverse stress the nibble paths
+    K, N, M = 1024, 256, 8
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(M, K, generator=g) * 0.5 + 6.0).to(torch.float16)
+    x[:, 7] = 300.0
+    for wv, zv in ((15, 0), (0, 15), (8, 8)):
+        qw = torch.from_numpy(O.pack_int4(np.full((K, N), wv)))
+        qz = torch.from_numpy(O.pack_int4(np.full((K // 128, N), zv)))
+        s = (torch.rand(K // 128, N, generator=g) * 9e-3 + 1e-3).to(torch.float16)
+        y = nq.awq_gemm(x.to(DEV), qw.to(DEV), s.to(DEV), qz.to(DEV), 8)
+        ref = O.w4a16_ref(x, qw, s, qz)
+        if wv == zv:
+            # exact answer is 0; what remains is fp32 cancellation against s*z*sum|x|
+            assert float(y.float().abs().max()) <= 1e-4 * 1e-2 * 8 * float(x.float().abs().sum(1).max())
+        else:
+            assert O.rel_err(y, ref) <= TIGHT, (wv, zv)
+
+
+@pytest.mark.parametrize("M", [256, 1024])
+def test_gemm_prefill_sizes_sampled_rows(M):
+    # full-size prefill shape; the oracle is evaluated on a sample of rows to stay fast
+    K, N = 4096, 4096
+    c = O.make_case(K, N, M, seed=M)
+    y = nq.awq_gemm(c["x"].to(DEV), c["qweight"].to(DEV), c["qscales"].to(DEV), c["qzeros"].to(DEV), 8)
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:48]
+    ref = O.w4a16_ref(c["x"][rows], c["qweight"], c["qscales"], c["qzeros"])
+    assert O.rel_err(y[rows.to(DEV)], ref) <= TIGHT
+
+
+def test_gemm_linearity_property_full_size():
+    # size-independent property at a full benchmark shape: y(2x) == 2*y(x) exactly in fp16
+    c = O.make_case(5120, 25600, 4, seed=3)
+    qw, s, qz = c["qweight"].to(DEV), c["qscales"].to(DEV), c["qzeros"].to(DEV)
+    x = c["x"].to(DEV)
+    y1 = nq.awq_gemm(x, qw, s, qz, 8)
+    y2 = nq.awq_gemm(x * 2, qw, s, qz, 8)
+    assert torch.equal(y2, y1 * 2)
