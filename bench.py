@@ -171,25 +171,24 @@ def run_ours(args):
             ys_host[(si, M)] = torch.empty(M, n, dtype=dtype).pin_memory()
     points = [(si, M) for M in MS for si in range(len(SHAPES))]  # M-major: a shape's reuses are far apart
 
-    def call(si, M, step, x):
-        lin = layers[si][step % len(layers[si])]
+    def call(si, M, copy, x):
+        lin = layers[si][copy % len(layers[si])]
         y = lin(x)
         if world > 1 and SHAPES[si][2] == "row":
             dist.all_reduce(y)
         return y
 
-    def sweep_device(step):
-        for (si, M) in points:
-            call(si, M, step, xs_dev[(si, M)])
+    # point j of a shape uses weight copy j, so a copy is reused only after the rest of the sweep
+    # (>1 GB of other weights) has gone through L2
+    def sweep_device(step=0):
+        for j, (si, M) in enumerate(points):
+            call(si, M, j // len(SHAPES) + step, xs_dev[(si, M)])
 
     def sweep_e2e(step):
-        last = None
-        for (si, M) in points:
+        for j, (si, M) in enumerate(points):
             x = xs_host[(si, M)].to(dev, non_blocking=True)
-            y = call(si, M, step, x)
+            y = call(si, M, j // len(SHAPES) + step, x)
             ys_host[(si, M)].copy_(y, non_blocking=True)
-            last = y
-        return last
 
     def barrier():
         torch.cuda.synchronize()
@@ -197,12 +196,25 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, offset):
+    def capture(fn):
+        """The launches of fn() as one CUDA graph (decode-sized calls are launch-bound from Python)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        return graph
+
+    def timed(fn, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for s in range(steps):
-            fn(offset + s)
+            fn(s)
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -212,14 +224,17 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
+    use_graph = world == 1  # NCCL calls stay outside graphs here
+    sweep_graph = capture(sweep_device) if use_graph else None
+    run_sweep = (lambda s: sweep_graph.replay()) if use_graph else sweep_device
     for w in range(max(args.warmup, 3)):
-        sweep_device(w)
+        run_sweep(w)
         sweep_e2e(w)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_dev = timed(sweep_device, args.steps, 100)
-    ms_e2e = timed(sweep_e2e, args.steps, 200)
+    ms_dev = timed(run_sweep, args.steps)
+    ms_e2e = timed(sweep_e2e, args.steps)
 
     # per-point pass: each point launched back to back over rotating weight copies
     per_point = []
@@ -227,13 +242,17 @@ def run_ours(args):
         K, N, kind = SHAPES[si]
         k, n = shard_shape(K, N, kind, world)
         reps = max(8, 2 * len(layers[si])) if M <= 128 else 4
+
+        def burst(si=si, M=M, reps=reps):
+            for r in range(reps):
+                call(si, M, r, xs_dev[(si, M)])
+        fn = capture(burst).replay if use_graph else burst
         for r in range(3):
-            call(si, M, r, xs_dev[(si, M)])
+            fn()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for r in range(reps):
-            call(si, M, r, xs_dev[(si, M)])
+        fn()
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / reps
@@ -275,7 +294,8 @@ def run_ours(args):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": "w4a16_gemm_sweep g128 M{1,4,16,128,1024,4096} x 5 (K,N) shapes (config 2)",
                        "points_per_step": len(points), "parallelism": f"tp{world}",
-                       "l2": "weights rotate over copies totalling >1.5x L2 per shape"},
+                       "l2": "weights rotate over copies totalling >1.5x L2 per shape",
+                       "launch": "device-timed sweep replayed as one CUDA graph; e2e through WQLinear_GEMM.forward"},
             "e2e": {"value": round(ms_e2e * 1e3 / args.steps, 2), "unit": "us", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": len(points) * args.steps,

@@ -79,8 +79,15 @@ int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const v
                 int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* Waits for `stream`, then returns the status the kernels recorded in this
+ * workspace: NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a bounded device-side wait
+ * (an mbarrier or a tile counter) gave up; the record is cleared.  The kernels
+ * never trap or spin without limit; this is how the host learns of a give-up.
+ * No counterpart in the reference (its Triton kernels have no waits). */
+int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* stream);
+
 /* Name of the kernel family nqb200_gemm would pick for this problem
- * ("decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
+ * ("decode_stream", "decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
 const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
 
 #ifdef __cplusplus

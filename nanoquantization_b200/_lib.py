@@ -26,6 +26,7 @@ SIGNATURES = {
     "nqb200_dequant": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nqb200_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
     "nqb200_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "nqb200_workspace_status": (_int, [_vp, _sz, _vp]),
     "nqb200_gemm_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _i64, _int]),
 }
 
@@ -109,3 +110,10 @@ def workspace(dev: torch.device, nbytes: int) -> torch.Tensor | None:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
         _workspaces[key] = ws
     return ws
+
+
+def check_workspaces() -> None:
+    """Synchronise and raise if any kernel recorded a give-up (a bounded wait that ran out)."""
+    lib = load()
+    for (_dev, stream), ws in list(_workspaces.items()):
+        check(lib.nqb200_workspace_status(ws.data_ptr(), ws.numel(), stream))

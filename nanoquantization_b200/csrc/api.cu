@@ -40,6 +40,7 @@ static int check_shape(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
 
 extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
+  if (stream_supports(M, N, K, g)) return stream_workspace_bytes(M, N, K);
   if (!decode_mma_supports(M, N, K, g)) return 0;
   const DecodePlan p = plan_decode(M, N, K, g);
   return p.ksplit > 1 ? p.counter_bytes + p.partial_bytes : 0;
@@ -47,6 +48,7 @@ extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, i
 
 extern "C" const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK) return "invalid";
+  if (stream_supports(M, N, K, g)) return "decode_stream";
   if (!decode_mma_supports(M, N, K, g)) return "generic";
   return "decode_mma";
 }
@@ -67,6 +69,24 @@ extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscal
   a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
+  if (stream_supports(M, N, K, g)) return launch_stream(a);
   if (decode_mma_supports(M, N, K, g)) return launch_decode_mma(a);
   return launch_generic(a);
+}
+
+extern "C" int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return NQB200_ERR_NULL_POINTER;
+  if (workspace_bytes < (size_t)kCounterBytes) return NQB200_ERR_WORKSPACE;
+  int* word = reinterpret_cast<int*>(workspace) + (kCounterBytes / 4 - 1);
+  int v = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(&v, word, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaGetLastError();
+    return NQB200_ERR_LAUNCH;
+  }
+  if (v != 0) {
+    if (cudaMemsetAsync(word, 0, sizeof(int), st) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  }
+  return v;
 }

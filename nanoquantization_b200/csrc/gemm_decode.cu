@@ -57,7 +57,10 @@ DecodePlan plan_decode(int64_t M, int64_t N, int64_t K, int64_t g) {
   if (want > G) want = G;
   p.gpc = (G + want - 1) / want;
   p.ksplit = (G + p.gpc - 1) / p.gpc;
-  p.counter_bytes = (((size_t)base * 4 + 255) / 256) * 256;
+  // the counters always occupy the same fixed head of the workspace, so that one call's
+  // partial sums can never be read as another call's counters
+  p.counter_bytes = kCounterBytes;
+  if (base * 4 > (int64_t)kCounterBytes) { p.gpc = G; p.ksplit = 1; }
   p.partial_bytes = p.ksplit > 1 ? (size_t)p.mchunks * p.ksplit * 8 * p.mt * (size_t)N * 4 : 0;
   return p;
 }

@@ -1,0 +1,363 @@
+// Streaming decode kernel: W4A16 skinny GEMM for up to 16 tokens, group size 128.
+//
+// One persistent CTA per SM.  The packed matrix is cut into units of 128 rows
+// (one quantisation group) by 512 columns; unit u = tile * G + group, so that a
+// CTA's contiguous range of units walks down K inside a column tile.  The 148
+// CTAs take equal contiguous ranges (sizes differ by at most one unit).
+//
+//   producer warp : for each unit, six TMA tensor loads into a 5-stage
+//                   shared-memory ring (two 128x128-byte boxes of packed
+//                   weights with the 128-byte swizzle, the group's scales and
+//                   zero-points, two boxes of activations), completion on an
+//                   mbarrier.  About 190 KB per SM is in flight from the
+//                   first cycle, which is what keeps HBM busy at these sizes.
+//   8 consumer warps : warp w owns columns 64w..64w+63 of the tile for the whole
+//                   group; arithmetic exactly as in the register-fed kernel
+//                   (raw nibbles as fp16 subnormals into mma.sync m16n8k16,
+//                   one extra all-ones mma for sum(x), scale and zero-point
+//                   applied once per group in fp32).  The 128-byte swizzle and
+//                   the mma's own k order (2t, 2t+1, 2t+8, 2t+9) make every
+//                   shared-memory load conflict-free.
+//
+// A CTA whose range covers a tile's whole K writes the output itself.  Other
+// segments go to a per-CTA slot (fp32) in the workspace; a counter per tile
+// finds the last contributor, which adds the slots in CTA order (so the result
+// does not depend on timing), adds the bias and writes the output.
+//
+// Every wait is bounded; on expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in
+// the workspace status word and drains instead of spinning.
+#include "common.cuh"
+#include "tma_utils.cuh"
+
+namespace nqb200 {
+
+constexpr int kStages = 5;
+constexpr int kUnitN = 512, kUnitK = 128;
+constexpr int kConsumerWarps = 8;
+constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
+constexpr int kOffW0 = 0, kOffW1 = 16384, kOffX0 = 32768, kOffX1 = 34816, kOffSc = 36864, kOffZ = 37888;
+constexpr int kStageBytes = 38912;
+constexpr int kStreamSmem = kStages * kStageBytes + 1024;
+constexpr int kSlotFloats = 16 * kUnitN;
+constexpr int kStatusWord = kCounterBytes / 4 - 1;  // last word of the counter region
+
+struct StreamParams {
+  const void* bias; int bias_dtype; uint16_t* out;
+  int M, N, G, ntiles, nctas;
+  long long U;
+  int* counters; float* slots;
+};
+
+bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
+  return M >= 1 && M <= 16 && g == 128 && K % 128 == 0 && N % 32 == 0 && (N + kUnitN - 1) / kUnitN < kStatusWord;
+}
+
+size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  (void)M;
+  const long long U = ((N + kUnitN - 1) / kUnitN) * (K / 128);
+  const long long C = U < kNumSMs ? U : kNumSMs;
+  return (size_t)kCounterBytes + (size_t)C * 2 * kSlotFloats * sizeof(float);
+}
+
+template <bool BF16>
+__device__ __forceinline__ void mma16816s(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  if (BF16) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+__device__ __forceinline__ long long cta_begin(long long c, long long U, long long C) { return (c * U) / C; }
+__device__ __forceinline__ int cta_of_unit(long long u, long long U, long long C) { return (int)(((u + 1) * C - 1) / U); }
+
+// value of column e (0..7) of a thread's 8-column group, row t of the token pair
+#define NQ_TOTAL_AT(tot, e, t) tot[((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) >> 1][2 * (((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) & 1) + (t)]
+
+template <int MT, bool BF16>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
+              const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x,
+              const StreamParams p) {
+  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
+  constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
+  constexpr float MULT_LO = BF16 ? 1.f : 16777216.f, MULT_HI = BF16 ? 1.f : 1048576.f, OFF = BF16 ? 128.f : 0.f;
+  constexpr uint32_t kStageTx = 2 * 16384 + 2 * (8 * MT * 128) + 1024 + 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_seg;
+  __shared__ int s_last;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long U = p.U, C = p.nctas;
+  const long long u_begin = cta_begin(blockIdx.x, U, C), u_end = cta_begin(blockIdx.x + 1, U, C);
+  const int nunits = (int)(u_end - u_begin);
+  const int G = p.G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kConsumerWarps); }
+    mbar_init(smem_u32(&bar_seg), kConsumerWarps);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z); prefetch_tmap(&tm_x);
+      int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nunits; ++i) {
+        const int s = i % kStages;
+        if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) { ok = false; break; }
+        const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
+        mbar_expect_tx(bar, kStageTx);
+        tma_load_2d(st + kOffW0, &tm_w, tile * 64, grp * kUnitK, bar);
+        tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, grp * kUnitK, bar);
+        tma_load_2d(st + kOffX0, &tm_x, grp * kUnitK, 0, bar);
+        tma_load_2d(st + kOffX1, &tm_x, grp * kUnitK + 64, 0, bar);
+        tma_load_2d(st + kOffSc, &tm_sc, tile * 256, grp, bar);
+        tma_load_2d(st + kOffZ, &tm_z, tile * 64, grp, bar);
+        ++issued;
+        if (++grp == G) { grp = 0; ++tile; }
+      }
+      if (!ok) atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      // do not leave while a copy of ours may still be landing in this CTA's shared memory
+      for (int i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
+        mbar_wait(smem_u32(&bar_full[i % kStages]), (i / kStages) & 1);
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  const int gq = lane >> 2, tig = lane & 3;
+  const int w = warp;
+  const int chunk = 2 * (w & 3) + (gq >> 2), inword = (gq & 3) * 4;
+  const uint32_t w_off = (w >> 2) ? kOffW1 : kOffW0;
+  // rows 16ks + 2tig + {0,1,8,9}: (row & 7) is 2tig or 2tig+1
+  const uint32_t sw_even = ((uint32_t)(chunk ^ ((2 * tig) & 7)) << 4) + inword;
+  const uint32_t sw_odd = ((uint32_t)(chunk ^ ((2 * tig + 1) & 7)) << 4) + inword;
+  const uint32_t row0 = (uint32_t)(2 * tig) * 128;
+
+  float total[MT][4][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) total[mt][b][i] = 0.f;
+
+  int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
+  const int first_tile = tile;
+  int seg_begin = grp;
+  uint32_t seg_phase = 0;
+  bool alive = true;
+
+  for (int i = 0; i < nunits && alive; ++i) {
+    const int s = i % kStages;
+    if (!mbar_wait(smem_u32(&bar_full[s]), (i / kStages) & 1)) {
+      atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      alive = false;
+      break;
+    }
+    const uint32_t st = smem_base + s * kStageBytes;
+    const uint32_t wb = st + w_off + row0;
+
+    float acc[MT][4][4], xs[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) xs[mt][q] = 0.f;
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[mt][b][q] = 0.f;
+    }
+
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint32_t rb = wb + ks * 16 * 128;
+      const uint32_t w0 = lds32(rb + sw_even), w1 = lds32(rb + 128 + sw_odd);
+      const uint32_t w2 = lds32(rb + 8 * 128 + sw_even), w3 = lds32(rb + 9 * 128 + sw_odd);
+      uint32_t xb0[MT], xb1[MT];
+      const uint32_t xbox = st + ((ks >> 2) ? kOffX1 : kOffX0);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const uint32_t xr = xbox + (uint32_t)(8 * mt + gq) * 128 + tig * 4;
+        xb0[mt] = lds32(xr + ((uint32_t)((2 * (ks & 3)) ^ gq) << 4));
+        xb1[mt] = lds32(xr + ((uint32_t)((2 * (ks & 3) + 1) ^ gq) << 4));
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t sel = (uint32_t)b | ((uint32_t)b << 4) | ((uint32_t)(4 + b) << 8) | ((uint32_t)(4 + b) << 12);
+        const uint32_t p01 = __byte_perm(w0, w1, sel), p23 = __byte_perm(w2, w3, sel);
+        uint32_t a0, a1, a2, a3;
+        if (BF16) {
+          a0 = (p01 & LO) | 0x43004300u; a1 = ((p01 >> 4) & LO) | 0x43004300u;
+          a2 = (p23 & LO) | 0x43004300u; a3 = ((p23 >> 4) & LO) | 0x43004300u;
+        } else {
+          a0 = p01 & LO; a1 = p01 & HI; a2 = p23 & LO; a3 = p23 & HI;
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) mma16816s<BF16>(acc[mt][b], a0, a1, a2, a3, xb0[mt], xb1[mt]);
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) mma16816s<BF16>(xs[mt], ONES, ONES, ONES, ONES, xb0[mt], xb1[mt]);
+    }
+
+    // scale, power of two and zero-point, once per group
+    {
+      const uint4 sv = lds128(st + kOffSc + (uint32_t)(64 * w + 8 * gq) * 2);
+      const uint32_t zw = lds32(st + kOffZ + (uint32_t)(8 * w + gq) * 4);
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int b = j >> 1, r = j & 1;
+        const int e = (j < 4) ? 2 * j : 2 * (j - 4) + 1;
+        const float sc = raw16_to_float<BF16>((uint16_t)((sw[e >> 1] >> (16 * (e & 1))) & 0xFFFF));
+        const float z = (float)((zw >> (4 * j)) & 0xF);
+        const float A = sc * (r ? MULT_HI : MULT_LO), B = sc * (z + OFF);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int t = 0; t < 2; ++t) total[mt][b][2 * r + t] += A * acc[mt][b][2 * r + t] - B * xs[mt][t];
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+
+    const bool tile_done = grp == G - 1;
+    if (tile_done || i == nunits - 1) {
+      const int n0 = tile * kUnitN + 64 * w + 8 * gq;
+      const bool n_ok = n0 < p.N;
+      if (seg_begin == 0 && tile_done) {
+        // this CTA saw the tile's whole K: write the output directly
+        if (n_ok) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int m = 8 * mt + 2 * tig + t;
+              if (m < p.M) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                  float v0 = NQ_TOTAL_AT(total[mt], e, t), v1 = NQ_TOTAL_AT(total[mt], e + 1, t);
+                  if (p.bias) { v0 += bias_to_float(p.bias, p.bias_dtype, n0 + e); v1 += bias_to_float(p.bias, p.bias_dtype, n0 + e + 1); }
+                  o[e >> 1] = (uint32_t)float_to_raw16<BF16>(v0) | ((uint32_t)float_to_raw16<BF16>(v1) << 16);
+                }
+                *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n0) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+        }
+      } else {
+        float* slot = p.slots + ((size_t)blockIdx.x * 2 + (tile == first_tile ? 0 : 1)) * kSlotFloats;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int m = 8 * mt + 2 * tig + t;
+            float* dst = slot + m * kUnitN + 64 * w + 8 * gq;
+            __stcg(reinterpret_cast<float4*>(dst), make_float4(NQ_TOTAL_AT(total[mt], 0, t), NQ_TOTAL_AT(total[mt], 1, t),
+                                                               NQ_TOTAL_AT(total[mt], 2, t), NQ_TOTAL_AT(total[mt], 3, t)));
+            __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(NQ_TOTAL_AT(total[mt], 4, t), NQ_TOTAL_AT(total[mt], 5, t),
+                                                                   NQ_TOTAL_AT(total[mt], 6, t), NQ_TOTAL_AT(total[mt], 7, t)));
+          }
+        __threadfence();
+        // all consumer warps have published their part of the slot
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
+        if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
+        seg_phase ^= 1;
+        const int first_cta = cta_of_unit((long long)tile * G, U, C);
+        const int last_cta = cta_of_unit((long long)tile * G + G - 1, U, C);
+        if (threadIdx.x == 0) s_last = (atomicAdd(p.counters + tile, 1) == last_cta - first_cta);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
+        if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
+        seg_phase ^= 1;
+        if (s_last) {
+          __threadfence();
+          const int tn0 = tile * kUnitN;
+          for (int idx = threadIdx.x; idx < p.M * (kUnitN / 4); idx += kConsumerWarps * 32) {
+            const int m = idx / (kUnitN / 4), c4 = (idx % (kUnitN / 4)) * 4;
+            if (tn0 + c4 < p.N) {
+              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int c = first_cta; c <= last_cta; ++c) {
+                const int which = (int)(cta_begin(c, U, C) / G) == tile ? 0 : 1;
+                const float4 q = __ldcg(reinterpret_cast<const float4*>(p.slots + ((size_t)c * 2 + which) * kSlotFloats + m * kUnitN + c4));
+                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+              }
+              if (p.bias) {
+                v.x += bias_to_float(p.bias, p.bias_dtype, tn0 + c4); v.y += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 1);
+                v.z += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 2); v.w += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 3);
+              }
+              const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
+              const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
+              *reinterpret_cast<uint2*>(p.out + (size_t)m * p.N + tn0 + c4) = make_uint2(o0, o1);
+            }
+          }
+          if (threadIdx.x == 0) p.counters[tile] = 0;  // leave the workspace as it was found
+        }
+        // s_last is next written after the first barrier round of the next segment end, which no
+        // warp can pass before every warp has read it here
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) total[mt][b][q] = 0.f;
+      seg_begin = 0;
+    }
+    if (++grp == G) { grp = 0; ++tile; }
+  }
+}
+
+template <int MT, bool BF16>
+static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx,
+                           const StreamParams& sp, cudaStream_t st) {
+  static bool configured = false;  // idempotent attribute; a repeated set from two threads is harmless
+  if (!configured) {
+    if (cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess) {
+      cudaGetLastError();
+      return NQB200_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  stream_kernel<MT, BF16><<<sp.nctas, kStreamThreads, kStreamSmem, st>>>(tw, ts, tz, tx, sp);
+  return check_launch();
+}
+
+int launch_stream(const GemmArgs& a) {
+  const int G = a.K / 128;
+  const int ntiles = (a.N + kUnitN - 1) / kUnitN;
+  const long long U = (long long)ntiles * G;
+  const int C = (int)(U < kNumSMs ? U : kNumSMs);
+  if (!a.ws || a.ws_bytes < stream_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
+  if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
+  const int mt = a.M > 8 ? 2 : 1;
+  alignas(64) CUtensorMap tw, ts, tz, tx;
+  const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, G, a.N / 2, 1, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, G, a.N / 8, 1, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && encode_2d(&tx, xdt, 2, a.x, a.M, a.K, 8 * mt, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return NQB200_ERR_LAUNCH;
+  StreamParams sp;
+  sp.bias = a.bias; sp.bias_dtype = a.bias_dtype; sp.out = (uint16_t*)a.out;
+  sp.M = a.M; sp.N = a.N; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = U;
+  sp.counters = (int*)a.ws; sp.slots = (float*)((char*)a.ws + kCounterBytes);
+  const bool bf = a.dtype == NQB200_BF16;
+  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, tx, sp, a.stream) : launch_stream_t<1, false>(tw, ts, tz, tx, sp, a.stream);
+  return bf ? launch_stream_t<2, true>(tw, ts, tz, tx, sp, a.stream) : launch_stream_t<2, false>(tw, ts, tz, tx, sp, a.stream);
+}
+
+}  // namespace nqb200

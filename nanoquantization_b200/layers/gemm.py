@@ -78,6 +78,9 @@ def awq_dequantize(
     return result
 
 
+_ws_bytes_cache: dict[tuple, int] = {}
+
+
 def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros: torch.Tensor,
            bias: torch.Tensor | None) -> torch.Tensor:
     """One fused call: out = x @ ((q - z) * s) (+ bias), any M."""
@@ -86,25 +89,38 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
     group_size = K // qscales.shape[0]
     dev = _lib.require_cuda(x, qweight, qscales, qzeros)
     _lib.require_b200(dev)
-    code = _lib.dtype_code(qscales.dtype)
-    if x.dtype != qscales.dtype:  # the reference casts x to the output dtype (gemm.py:259)
-        x = x.to(qscales.dtype)
+    dtype = qscales.dtype
+    code = _lib.dtype_code(dtype)
+    if x.dtype != dtype:  # the reference casts x to the output dtype (gemm.py:259)
+        x = x.to(dtype)
     x, qweight, qscales, qzeros = _contig(x), _contig(qweight), _contig(qscales), _contig(qzeros)
     bias_ptr, bias_code = None, 0
     if bias is not None:
         bias = _contig(bias)
         bias_ptr, bias_code = bias.data_ptr(), _lib.dtype_code(bias.dtype)
-    out = torch.empty(M, N, dtype=qscales.dtype, device=dev)
+    out = torch.empty(M, N, dtype=dtype, device=dev)
     if M == 0:
         return out
     lib = _lib.load()
-    with torch.cuda.device(dev):
-        nbytes = lib.nqb200_gemm_workspace_bytes(M, N, K, group_size, code)
+    key = (M, N, K, group_size, code)
+    nbytes = _ws_bytes_cache.get(key)
+    if nbytes is None:
+        nbytes = _ws_bytes_cache[key] = lib.nqb200_gemm_workspace_bytes(M, N, K, group_size, code)
+    other_device = dev.index is not None and dev.index != torch.cuda.current_device()
+    if other_device:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
         ws = _lib.workspace(dev, nbytes)
-        _lib.check(lib.nqb200_gemm(x.data_ptr(), qweight.data_ptr(), qscales.data_ptr(), qzeros.data_ptr(),
-                                   bias_ptr, bias_code, out.data_ptr(), M, N, K, group_size, code,
-                                   ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-                                   _lib.stream_ptr()))
+        status = lib.nqb200_gemm(x.data_ptr(), qweight.data_ptr(), qscales.data_ptr(), qzeros.data_ptr(),
+                                 bias_ptr, bias_code, out.data_ptr(), M, N, K, group_size, code,
+                                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                 _lib.stream_ptr())
+    finally:
+        if other_device:
+            torch.cuda.set_device(prev)
+    if status:
+        _lib.check(status)
     return out
 
 

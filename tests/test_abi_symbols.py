@@ -45,5 +45,10 @@ def test_host_only_entry_points():
     mis = ctypes.addressof(buf) | 8
     assert lib.nqb200_unpack_int4(mis, mis, 1, 1, None) == 3
     assert lib.nqb200_gemm_workspace_bytes(1, 4096, 4096, 128, 0) > 0
-    assert lib.nqb200_gemm_kernel_name(1, 4096, 4096, 128, 0) in (b"decode_mma",)
+    assert lib.nqb200_gemm_kernel_name(1, 4096, 4096, 128, 0) in (b"decode_stream",)
     assert lib.nqb200_gemm_kernel_name(1, 24, 100, 100, 0) == b"generic"
+
+
+def test_library_is_not_older_than_its_sources():
+    from nanoquantization_b200.csrc import build
+    assert not build._stale(), "libnqb200.so is older than csrc/: rebuild with python -m nanoquantization_b200.csrc.build"
