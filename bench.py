@@ -388,14 +388,56 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_point(args):
+    """One (M, K, N) point launched --reps times over rotating weight copies, timed with CUDA
+    events; the small, single-kernel case profilers are pointed at."""
+    import nanoquantization_b200 as nq  # noqa: F401
+    from nanoquantization_b200 import _lib
+    M, K, N = (int(v) for v in args.point.split(","))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    ncopy = max(2, -(-int(1.5 * L2_BYTES) // weight_bytes(K, N)))
+    layers = [make_layer(K, N, 7 + c, dev, dtype) for c in range(ncopy)]
+    x = torch.randn(M, K, device=dev).to(dtype)
+    def burst():
+        for r in range(args.reps):
+            layers[r % ncopy](x)
+    burst()
+    torch.cuda.synchronize()
+    fn = burst
+    if not args.no_graph:  # replayed as one CUDA graph so that the number is device time, not Python launch time
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            burst()
+        fn = graph.replay
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.check_workspaces()
+    us = e0.elapsed_time(e1) * 1e3 / args.reps
+    print(json.dumps({"point": [M, K, N], "reps": args.reps, "us_per_call_incl_launch": round(us, 2),
+                      "kernel": _lib.load().nqb200_gemm_kernel_name(M, N, K, GROUP, 0).decode()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--point", default=None, help="M,K,N: run only this point (for profilers)")
+    ap.add_argument("--reps", type=int, default=6)
+    ap.add_argument("--no-graph", action="store_true", help="with --point: plain launches (what a profiler should see)")
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.point:
+        run_point(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

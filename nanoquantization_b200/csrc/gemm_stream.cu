@@ -31,20 +31,31 @@
 
 namespace nqb200 {
 
-constexpr int kStages = 5;
 constexpr int kUnitN = 512, kUnitK = 128;
 constexpr int kConsumerWarps = 8;
 constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
-constexpr int kOffW0 = 0, kOffW1 = 16384, kOffX0 = 32768, kOffX1 = 34816, kOffSc = 36864, kOffZ = 37888;
-constexpr int kStageBytes = 38912;
-constexpr int kStreamSmem = kStages * kStageBytes + 1024;
-constexpr int kSlotFloats = 16 * kUnitN;
+constexpr int kOffW0 = 0, kOffW1 = 16384, kOffX0 = 32768;
+
+// Up to 8 tokens (MT = 1): two CTAs per SM with three stages each, so that 16 consumer warps
+// share an SM's issue slots.  Up to 16 tokens (MT = 2): one CTA per SM with five stages.
+template <int MT> struct StreamCfg {
+  static constexpr int kCtasPerSm = MT == 1 ? 2 : 1;
+  static constexpr int kStages = MT == 1 ? 3 : 5;
+  static constexpr int kXBox = 8 * MT * 128;                 // bytes of one activation box
+  static constexpr int kOffX1 = kOffX0 + kXBox;
+  static constexpr int kOffSc = kOffX0 + 2 * kXBox;
+  static constexpr int kOffZ = kOffSc + 1024;
+  static constexpr int kStageBytes = (kOffZ + 256 + 1023) / 1024 * 1024;
+  static constexpr int kSmem = kStages * kStageBytes + 1024;
+  static constexpr int kSlotFloats = 8 * MT * kUnitN;
+  static constexpr uint32_t kStageTx = 2 * 16384 + 2 * kXBox + 1024 + 256;
+};
 constexpr int kStatusWord = kCounterBytes / 4 - 1;  // last word of the counter region
 
 struct StreamParams {
   const void* bias; int bias_dtype; uint16_t* out;
   int M, N, G, ntiles, nctas;
-  long long U;
+  uint32_t U;
   int* counters; float* slots;
 };
 
@@ -53,50 +64,57 @@ bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
 }
 
 size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  (void)M;
   const long long U = ((N + kUnitN - 1) / kUnitN) * (K / 128);
-  const long long C = U < kNumSMs ? U : kNumSMs;
-  return (size_t)kCounterBytes + (size_t)C * 2 * kSlotFloats * sizeof(float);
+  const long long cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
+  const long long C = U < cap ? U : cap;
+  return (size_t)kCounterBytes + (size_t)C * 2 * (size_t)(M > 8 ? 16 : 8) * kUnitN * sizeof(float);
 }
 
 template <bool BF16>
 __device__ __forceinline__ void mma16816s(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
   if (BF16) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   } else {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   }
 }
 
-__device__ __forceinline__ long long cta_begin(long long c, long long U, long long C) { return (c * U) / C; }
-__device__ __forceinline__ int cta_of_unit(long long u, long long U, long long C) { return (int)(((u + 1) * C - 1) / U); }
+// unit ranges in 32-bit arithmetic (the host checks U * C < 2^31): 64-bit division is a long
+// dependent instruction sequence on the GPU and these run on the critical path of the tail
+__device__ __forceinline__ uint32_t cta_begin(uint32_t c, uint32_t U, uint32_t C) { return (c * U) / C; }
+__device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t U, uint32_t C) { return (int)(((u + 1) * C - 1) / U); }
 
 // value of column e (0..7) of a thread's 8-column group, row t of the token pair
 #define NQ_TOTAL_AT(tot, e, t) tot[((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) >> 1][2 * (((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) & 1) + (t)]
 
 template <int MT, bool BF16>
-__global__ void __launch_bounds__(kStreamThreads, 1)
+__global__ void __launch_bounds__(kStreamThreads, StreamCfg<MT>::kCtasPerSm)
 stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
               const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x,
               const StreamParams p) {
   constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
   constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
   constexpr float MULT_LO = BF16 ? 1.f : 16777216.f, MULT_HI = BF16 ? 1.f : 1048576.f, OFF = BF16 ? 128.f : 0.f;
-  constexpr uint32_t kStageTx = 2 * 16384 + 2 * (8 * MT * 128) + 1024 + 256;
+  using Cfg = StreamCfg<MT>;
+  constexpr int kStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kOffX1 = Cfg::kOffX1, kOffSc = Cfg::kOffSc,
+                kOffZ = Cfg::kOffZ, kSlotFloats = Cfg::kSlotFloats;
+  constexpr uint32_t kStageTx = Cfg::kStageTx;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_seg;
   __shared__ int s_last;
+  __shared__ int s_slot[2 * kNumSMs];  // slot of each contributor of the tile being finalised
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // same place, generic pointer
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long U = p.U, C = p.nctas;
-  const long long u_begin = cta_begin(blockIdx.x, U, C), u_end = cta_begin(blockIdx.x + 1, U, C);
+  const uint32_t U = p.U, C = (uint32_t)p.nctas;
+  const uint32_t u_begin = cta_begin(blockIdx.x, U, C), u_end = cta_begin(blockIdx.x + 1, U, C);
   const int nunits = (int)(u_end - u_begin);
   const int G = p.G;
 
@@ -167,8 +185,8 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       alive = false;
       break;
     }
-    const uint32_t st = smem_base + s * kStageBytes;
-    const uint32_t wb = st + w_off + row0;
+    const uint8_t* st = smem_gen + s * kStageBytes;
+    const uint8_t* wb = st + w_off + row0;
 
     float acc[MT][4][4], xs[MT][4];
 #pragma unroll
@@ -183,16 +201,16 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      const uint32_t rb = wb + ks * 16 * 128;
-      const uint32_t w0 = lds32(rb + sw_even), w1 = lds32(rb + 128 + sw_odd);
-      const uint32_t w2 = lds32(rb + 8 * 128 + sw_even), w3 = lds32(rb + 9 * 128 + sw_odd);
+      const uint8_t* rb = wb + ks * 16 * 128;
+      const uint32_t w0 = lds32(rb, sw_even), w1 = lds32(rb, 128 + sw_odd);
+      const uint32_t w2 = lds32(rb, 8 * 128 + sw_even), w3 = lds32(rb, 9 * 128 + sw_odd);
       uint32_t xb0[MT], xb1[MT];
-      const uint32_t xbox = st + ((ks >> 2) ? kOffX1 : kOffX0);
+      const uint8_t* xbox = st + ((ks >> 2) ? kOffX1 : kOffX0);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const uint32_t xr = xbox + (uint32_t)(8 * mt + gq) * 128 + tig * 4;
-        xb0[mt] = lds32(xr + ((uint32_t)((2 * (ks & 3)) ^ gq) << 4));
-        xb1[mt] = lds32(xr + ((uint32_t)((2 * (ks & 3) + 1) ^ gq) << 4));
+        const uint8_t* xr = xbox + (uint32_t)(8 * mt + gq) * 128 + tig * 4;
+        xb0[mt] = lds32(xr, (uint32_t)((2 * (ks & 3)) ^ gq) << 4);
+        xb1[mt] = lds32(xr, (uint32_t)((2 * (ks & 3) + 1) ^ gq) << 4);
       }
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
@@ -214,8 +232,8 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 
     // scale, power of two and zero-point, once per group
     {
-      const uint4 sv = lds128(st + kOffSc + (uint32_t)(64 * w + 8 * gq) * 2);
-      const uint32_t zw = lds32(st + kOffZ + (uint32_t)(8 * w + gq) * 4);
+      const uint4 sv = lds128(st, kOffSc + (uint32_t)(64 * w + 8 * gq) * 2);
+      const uint32_t zw = lds32(st, kOffZ + (uint32_t)(8 * w + gq) * 4);
       const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -264,7 +282,7 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             const int m = 8 * mt + 2 * tig + t;
-            float* dst = slot + m * kUnitN + 64 * w + 8 * gq;
+            float* dst = slot + m * kUnitN + 64 * w + 8 * gq;  // rows beyond M are scratch inside the slot
             __stcg(reinterpret_cast<float4*>(dst), make_float4(NQ_TOTAL_AT(total[mt], 0, t), NQ_TOTAL_AT(total[mt], 1, t),
                                                                NQ_TOTAL_AT(total[mt], 2, t), NQ_TOTAL_AT(total[mt], 3, t)));
             __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(NQ_TOTAL_AT(total[mt], 4, t), NQ_TOTAL_AT(total[mt], 5, t),
@@ -276,8 +294,8 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
         if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
         seg_phase ^= 1;
-        const int first_cta = cta_of_unit((long long)tile * G, U, C);
-        const int last_cta = cta_of_unit((long long)tile * G + G - 1, U, C);
+        const int first_cta = cta_of_unit((uint32_t)tile * G, U, C);
+        const int last_cta = cta_of_unit((uint32_t)tile * G + G - 1, U, C);
         if (threadIdx.x == 0) s_last = (atomicAdd(p.counters + tile, 1) == last_cta - first_cta);
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
@@ -285,15 +303,30 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         seg_phase ^= 1;
         if (s_last) {
           __threadfence();
+          for (int c = first_cta + (int)threadIdx.x; c <= last_cta; c += kConsumerWarps * 32)
+            s_slot[c - first_cta] = 2 * c + ((int)(cta_begin(c, U, C) / G) == tile ? 0 : 1);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
+        if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
+        seg_phase ^= 1;
+        if (s_last) {
           const int tn0 = tile * kUnitN;
+          const int ncontrib = last_cta - first_cta + 1;
           for (int idx = threadIdx.x; idx < p.M * (kUnitN / 4); idx += kConsumerWarps * 32) {
             const int m = idx / (kUnitN / 4), c4 = (idx % (kUnitN / 4)) * 4;
             if (tn0 + c4 < p.N) {
+              const float* src = p.slots + m * kUnitN + c4;
               float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int c = first_cta; c <= last_cta; ++c) {
-                const int which = (int)(cta_begin(c, U, C) / G) == tile ? 0 : 1;
-                const float4 q = __ldcg(reinterpret_cast<const float4*>(p.slots + ((size_t)c * 2 + which) * kSlotFloats + m * kUnitN + c4));
-                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+              // loads of eight contributors are in flight together; the additions stay in CTA order
+              for (int c0 = 0; c0 < ncontrib; c0 += 8) {
+                float4 q[8];
+#pragma unroll
+                for (int d = 0; d < 8; ++d)
+                  q[d] = c0 + d < ncontrib ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)s_slot[c0 + d] * kSlotFloats))
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int d = 0; d < 8; ++d) { v.x += q[d].x; v.y += q[d].y; v.z += q[d].z; v.w += q[d].w; }
               }
               if (p.bias) {
                 v.x += bias_to_float(p.bias, p.bias_dtype, tn0 + c4); v.y += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 1);
@@ -306,8 +339,8 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
           }
           if (threadIdx.x == 0) p.counters[tile] = 0;  // leave the workspace as it was found
         }
-        // s_last is next written after the first barrier round of the next segment end, which no
-        // warp can pass before every warp has read it here
+        // s_last and s_slot are next written after the first barrier round of the next segment
+        // end, which no warp can pass before every warp is done with them here
       }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -324,12 +357,14 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 template <int MT, bool BF16>
 static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx,
                            const StreamParams& sp, cudaStream_t st) {
+  constexpr int kStreamSmem = StreamCfg<MT>::kSmem;
   static bool configured = false;  // idempotent attribute; a repeated set from two threads is harmless
   if (!configured) {
     if (cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess) {
       cudaGetLastError();
       return NQB200_ERR_LAUNCH;
     }
+    cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   stream_kernel<MT, BF16><<<sp.nctas, kStreamThreads, kStreamSmem, st>>>(tw, ts, tz, tx, sp);
@@ -340,10 +375,12 @@ int launch_stream(const GemmArgs& a) {
   const int G = a.K / 128;
   const int ntiles = (a.N + kUnitN - 1) / kUnitN;
   const long long U = (long long)ntiles * G;
-  const int C = (int)(U < kNumSMs ? U : kNumSMs);
+  if (U * 2 * kNumSMs >= (1ll << 31)) return NQB200_ERR_TOO_LARGE;
+  const int mt = a.M > 8 ? 2 : 1;
+  const long long cap = (long long)kNumSMs * (mt == 1 ? 2 : 1);
+  const int C = (int)(U < cap ? U : cap);
   if (!a.ws || a.ws_bytes < stream_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
   if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
-  const int mt = a.M > 8 ? 2 : 1;
   alignas(64) CUtensorMap tw, ts, tz, tx;
   const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -353,7 +390,7 @@ int launch_stream(const GemmArgs& a) {
   if (!ok) return NQB200_ERR_LAUNCH;
   StreamParams sp;
   sp.bias = a.bias; sp.bias_dtype = a.bias_dtype; sp.out = (uint16_t*)a.out;
-  sp.M = a.M; sp.N = a.N; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = U;
+  sp.M = a.M; sp.N = a.N; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = (uint32_t)U;
   sp.counters = (int*)a.ws; sp.slots = (float*)((char*)a.ws + kCounterBytes);
   const bool bf = a.dtype == NQB200_BF16;
   if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, tx, sp, a.stream) : launch_stream_t<1, false>(tw, ts, tz, tx, sp, a.stream);

@@ -80,11 +80,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr)); return v;
+// Plain C++ loads from shared memory: the compiler may schedule them freely between the
+// barrier waits (which clobber memory), which is what lets it hoist a whole group's loads.
+__device__ __forceinline__ uint32_t lds32(const uint8_t* base, uint32_t off) {
+  return *reinterpret_cast<const uint32_t*>(base + off);
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)); return v;
+__device__ __forceinline__ uint4 lds128(const uint8_t* base, uint32_t off) {
+  return *reinterpret_cast<const uint4*>(base + off);
 }
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
