@@ -79,6 +79,25 @@ int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const v
                 int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* nqb200_gemm for up to 16 tokens without any device allocation by anyone.
+ * It has no counterpart in the reference.  It is for callers that cannot
+ * provide a scratch buffer because they cannot allocate: hosts that own all
+ * device memory themselves (a serving engine whose KV-cache pool already holds
+ * every free byte, a plugin interface without an allocator in which a
+ * cudaMalloc from the plugin is an error).  The scratch is a fixed array inside
+ * the library, about 9.4 MiB, resident on every GPU that loads the library
+ * until the process exits.  Limits: 1 <= M <= 16, group_size == 128,
+ * N % 32 == 0; anything else returns NQB200_ERR_TOO_LARGE (NQB200_ERR_BAD_SHAPE
+ * for sizes no entry point accepts).  It calls no cudaMalloc, cudaFree or other
+ * allocating routine.  The first call on a device looks up the array's device
+ * address (with that device current); make that first call outside any stream
+ * capture.  All calls share the one array: calls that can overlap on the GPU
+ * (different streams, no dependency between them) race and must be serialised
+ * by the caller.  Results are bit-identical to nqb200_gemm for the same inputs. */
+int nqb200_gemm_decode_noalloc(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                               const void* bias, int bias_dtype, void* out,
+                               int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype, void* stream);
+
 /* Waits for `stream`, then returns the status the kernels recorded in this
  * workspace: NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a bounded device-side wait
  * (an mbarrier or a tile counter) gave up; the record is cleared.  The kernels

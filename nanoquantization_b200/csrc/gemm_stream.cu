@@ -28,6 +28,7 @@
 // the workspace status word and drains instead of spinning.
 #include "common.cuh"
 #include "tma_utils.cuh"
+#include <mutex>
 
 namespace nqb200 {
 
@@ -398,3 +399,82 @@ int launch_stream(const GemmArgs& a) {
 }
 
 }  // namespace nqb200
+
+// ---------------------------------------------------------------------------
+// Decode GEMM for callers that may not allocate device memory.
+//
+// Some hosts of this library own every byte of device memory themselves: a
+// serving engine that has already handed all free HBM to its KV-cache pool, or
+// a plugin interface that gives the plugin no allocator and treats a cudaMalloc
+// from inside it as an error.  Such a caller cannot create the scratch buffer
+// that nqb200_gemm expects.  For them the scratch of the streaming decode kernel
+// lives in the fixed array below, which every GPU that loads this library
+// holds from load until exit (kNoAllocScratchBytes, about 9.4 MiB).
+//
+// The name `g_noalloc_scratch` is only a host-side handle here, not a device
+// address; the device address is fetched once per device with
+// cudaGetSymbolAddress (with that device current) and passed to the kernel.
+// ---------------------------------------------------------------------------
+namespace nqb200 {
+// counters + two slots for each of the 296 CTAs of the 8-token configuration (the 16-token
+// configuration needs the same: 148 CTAs with slots twice the size)
+constexpr size_t kNoAllocScratchBytes = (size_t)kCounterBytes + (size_t)2 * kNumSMs * 2 * 8 * kUnitN * sizeof(float);
+constexpr int kMaxDevices = 64;
+}  // namespace nqb200
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[nqb200::kNoAllocScratchBytes];
+
+static void* noalloc_scratch_for_current_device(int* status) {
+  static std::mutex mu;
+  static void* ptrs[nqb200::kMaxDevices] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= nqb200::kMaxDevices) {
+    cudaGetLastError();
+    *status = NQB200_ERR_UNSUPPORTED_DEVICE;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) {
+      cudaGetLastError();
+      *status = NQB200_ERR_LAUNCH;
+      return nullptr;
+    }
+    ptrs[dev] = ptr;
+  }
+  return ptrs[dev];
+}
+
+extern "C" int nqb200_gemm_decode_noalloc(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                                          const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
+                                          int64_t group_size, int dtype, void* stream) {
+  using namespace nqb200;
+  if (M < 0 || N <= 0 || K <= 0 || group_size <= 0 || K % group_size != 0 || N % 8 != 0) return NQB200_ERR_BAD_SHAPE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  if (M == 0) return NQB200_OK;
+  // beyond what the fixed scratch was sized for: more than 16 tokens, or a shape the streaming
+  // kernel does not take (it needs group size 128 and N a multiple of 32)
+  if (M > 16 || !stream_supports(M, N, K, group_size) || stream_workspace_bytes(M, N, K) > kNoAllocScratchBytes)
+    return NQB200_ERR_TOO_LARGE;
+  if (!x || !qweight || !qscales || !qzeros || !out) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(qscales) || !aligned16(qzeros) || !aligned16(out) ||
+      (bias && !aligned16(bias)))
+    return NQB200_ERR_MISALIGNED;
+  if (bias && bias_dtype != NQB200_F16 && bias_dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  int st = NQB200_OK;
+  void* scratch = noalloc_scratch_for_current_device(&st);
+  if (!scratch) return st;
+  // the array keeps whatever the previous call left; the tile counters and the status word must
+  // start at zero (a memset on the caller's stream, no allocation)
+  if (cudaMemsetAsync(scratch, 0, kCounterBytes, (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return NQB200_ERR_LAUNCH;
+  }
+  GemmArgs a;
+  a.x = x; a.qw = (const uint32_t*)qweight; a.sc = qscales; a.qz = (const uint32_t*)qzeros;
+  a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)group_size; a.dtype = dtype;
+  a.ws = scratch; a.ws_bytes = kNoAllocScratchBytes; a.stream = (cudaStream_t)stream;
+  return launch_stream(a);
+}
