@@ -1,0 +1,332 @@
+// Prefill kernel on the 5th-generation tensor cores: W4A16 GEMM for more than
+// 16 tokens, group size 128, bound by the tensor pipe (and, below a few hundred
+// tokens, by HBM).
+//
+//   D[n, tok] (TMEM, fp32) = sum_k W[k, n] (TMEM, 16-bit) * x[tok, k] (smem)
+//
+// The weights are the 128-row A operand, dequantised to their true 16-bit
+// values (q - z) * s -- the integer difference first, then one multiply, which
+// is the reference's rounding -- straight from registers into tensor memory;
+// the tokens are the N dimension (up to 128 per tile), read from shared memory
+// as a K-major operand that TMA wrote with the 128-byte swizzle.  A packed word
+// never touches shared memory again after the TMA load, and a dequantised
+// value never touches shared memory at all.
+//
+// Persistent CTAs, one per SM, walk output tiles of 256 weight columns x 128
+// tokens (token tiles of one column tile go to neighbouring CTAs so that they
+// share the packed weights in L2).  Per tile, for each group of 128 k:
+//
+//   warp 0        TMA producer: 128 x 128 B of packed weights, two 128 x 64
+//                 boxes of activations, the group's scales and zero-points.
+//   warps 2-17    dequantisers, two sets of 8 taking alternate groups.  Warp
+//                 (quarter q, half h) turns words 8q..8q+7 of k-steps 4h..4h+3
+//                 into operand registers: PRMT pairs byte b of rows k and k+1,
+//                 LOP3 makes 1024+q (fp16) or 128+q (bf16), HSUB2 removes
+//                 1024+z, HMUL2 applies the scale; tcgen05.st.16x128b.x2 puts
+//                 byte b into lanes 16*(b&1).. of its lane quarter of A block
+//                 b>>1.
+//   warp 1        MMA issuer: per k-step two tcgen05.mma (M=128, N=tokens,
+//                 K=16), accumulating over all of K in tensor memory.
+//   warps 18-21   epilogue at the end of a tile: D -> registers -> bias ->
+//                 16-bit -> out[tok, n].
+//
+// Every wait is bounded; on expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in
+// the workspace status word (when a workspace is given), all roles drain, and
+// tensor memory is released.
+#include "common.cuh"
+#include "tma_utils.cuh"
+#include "umma_utils.cuh"
+
+namespace nqb200 {
+namespace pre {
+
+constexpr int kTileN = 256, kTileT = 128, kUnitK = 128;
+constexpr int kStages = 4, kAStages = 2;
+constexpr int kDequantWarps = 16, kEpiWarps = 4;
+constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;
+constexpr int kOffW = 0, kOffX0 = 16384, kOffX1 = 32768, kOffSc = 49152, kOffZ = 49664, kStageBytes = 50176;
+constexpr int kSmem = kStages * kStageBytes + 1024;
+constexpr uint32_t kStageTx = 16384 + 2 * 16384 + 512 + 128;
+constexpr int kColA = 0, kColD = 256, kTmemCols = 512;
+
+struct Params {
+  const void* bias; int bias_dtype; uint16_t* out;
+  int M, N, G, ntiles_n, ntiles_t, nt;  // nt: MMA N (tokens per tile rounded up to 16)
+  int* status;                          // may be null
+};
+
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  const uint32_t b = smem_u32(bar);
+  if (mbar_try_wait(b, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(b, parity)) return true;
+    if ((i & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicExch(status, NQB200_ERR_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+template <bool BF16> __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (BF16) asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (BF16) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
+                    const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x, const Params p) {
+  constexpr uint32_t LO = 0x000F000Fu;
+  constexpr uint32_t MAGIC = BF16 ? 0x43004300u : 0x64006400u;  // 128.0 / 1024.0 in both halves
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_afull[kAStages], bar_aempty[kAStages],
+      bar_dfull, bar_dempty, bar_drain;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort_i;
+
+  volatile int* s_abort = &s_abort_i;
+  int* status = p.status;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.G;
+  const int ntiles = p.ntiles_n * p.ntiles_t;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kDequantWarps / 2 + 1); }
+    for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&bar_afull[s]), kDequantWarps / 2); mbar_init(smem_u32(&bar_aempty[s]), 1); }
+    mbar_init(smem_u32(&bar_dfull), 1);
+    mbar_init(smem_u32(&bar_dempty), kEpiWarps);
+    mbar_init(smem_u32(&bar_drain), 1);
+    s_abort_i = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&s_tmem), kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  // Units are numbered consecutively over this CTA's tiles: unit i belongs to local tile i / G.
+  // Tile t (global) = blockIdx.x + j * gridDim.x; token tile index varies fastest.
+  int my_tiles = 0;
+  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) ++my_tiles;
+  const int nunits = my_tiles * G;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z); prefetch_tmap(&tm_x);
+      int issued = 0, i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+        const int tile_n = t / p.ntiles_t, tile_t = t % p.ntiles_t;
+        for (int grp = 0; grp < G; ++grp, ++i) {
+          const int s = i % kStages;
+          if (i >= kStages && !wait_bar(&bar_empty[s], ((i / kStages) - 1) & 1, s_abort, status)) { ok = false; break; }
+          const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
+          mbar_expect_tx(bar, kStageTx);
+          tma_load_2d(st + kOffW, &tm_w, tile_n * 32, grp * kUnitK, bar);
+          tma_load_2d(st + kOffX0, &tm_x, grp * kUnitK, tile_t * kTileT, bar);
+          tma_load_2d(st + kOffX1, &tm_x, grp * kUnitK + 64, tile_t * kTileT, bar);
+          tma_load_2d(st + kOffSc, &tm_sc, tile_n * 128, grp, bar);
+          tma_load_2d(st + kOffZ, &tm_z, tile_n * 32, grp, bar);
+          ++issued;
+        }
+      }
+      // do not leave while a copy of ours may still be landing in this CTA's shared memory
+      for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j)
+        mbar_wait(smem_u32(&bar_full[j % kStages]), (j / kStages) & 1);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(BF16 ? 1 : 0, 128, p.nt);
+      bool ok = true;
+      for (int i = 0; i < nunits && ok; ++i) {
+        const int s = i % kStages, sa = i % kAStages;
+        const int grp = i % G, lt = i / G;
+        if (grp == 0 && lt > 0 && !wait_bar(&bar_dempty, (lt - 1) & 1, s_abort, status)) break;  // epilogue drained D
+        if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) break;
+        if (!wait_bar(&bar_afull[sa], (i / kAStages) & 1, s_abort, status)) break;
+        tc_fence_after();
+        const uint32_t xaddr = smem_base + s * kStageBytes + kOffX0;
+        const uint32_t a0 = tmem + kColA + sa * 128, a1 = a0 + 64, d = tmem + kColD;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t bdesc = umma_smem_desc_sw128(xaddr + (ks >> 2) * 16384 + (ks & 3) * 32);
+          const uint32_t acc = (grp > 0 || ks > 0) ? 1u : 0u;
+          umma_ts(d, a0 + ks * 8, bdesc, idesc, acc);
+          umma_ts(d + 128, a1 + ks * 8, bdesc, idesc, acc);
+        }
+        umma_commit(smem_u32(&bar_aempty[sa]));
+        umma_commit(smem_u32(&bar_empty[s]));
+        if (grp == G - 1) umma_commit(smem_u32(&bar_dfull));
+      }
+      // everything issued has completed before tensor memory may be released
+      umma_commit(smem_u32(&bar_drain));
+      mbar_wait(smem_u32(&bar_drain), 0);
+    }
+  } else if (warp < 2 + kDequantWarps) {
+    // -------------------------------------------------------------- dequantisers
+    const int dw = warp - 2;
+    const int q = warp & 3, h = (dw >> 2) & 1, set = dw >> 3;  // set: which units (even / odd) this warp serves
+    const int gq = lane >> 2, tig = lane & 3;
+    const int chunk = 2 * q + (gq >> 2), inword = (gq & 3) * 4;
+    const uint32_t sw_even = ((uint32_t)(chunk ^ ((2 * tig) & 7)) << 4) + inword;
+    const uint32_t sw_odd = ((uint32_t)(chunk ^ ((2 * tig + 1) & 7)) << 4) + inword;
+    const uint32_t row0 = (uint32_t)(2 * tig) * 128;
+    const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
+    for (int i = set; i < nunits; i += 2) {
+      const int s = i % kStages, sa = i % kAStages;  // kAStages == 2: sa == set
+      if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) break;
+      const uint8_t* st = smem_gen + s * kStageBytes;
+      // per column of this thread's word: the scale and 1024+z (128+z), each in both halves
+      uint32_t sc2[8], zm2[8];
+      {
+        const uint4 sv = lds128(st, kOffSc + (uint32_t)(64 * q + 8 * gq) * 2);
+        const uint32_t zw = lds32(st, kOffZ + (uint32_t)(8 * q + gq) * 4);
+        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int e = (j < 4) ? 2 * j : 2 * (j - 4) + 1;  // column held by nibble j
+          sc2[j] = (e & 1) ? __byte_perm(sw[e >> 1], 0, 0x3232) : __byte_perm(sw[e >> 1], 0, 0x1010);
+          const uint32_t z = (zw >> (4 * j)) & 0xFu;
+          zm2[j] = (z | (z << 16)) | MAGIC;
+        }
+      }
+      if (i >= kAStages && !wait_bar(&bar_aempty[sa], ((i / kAStages) - 1) & 1, s_abort, status)) break;
+      tc_fence_after();
+      const uint8_t* wb = st + kOffW + row0;
+      const uint32_t acol = lane_base + kColA + sa * 128;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const int ks = 4 * h + kk;
+        const uint8_t* rb = wb + ks * 16 * 128;
+        const uint32_t w0 = lds32(rb, sw_even), w1 = lds32(rb, 128 + sw_odd);
+        const uint32_t w2 = lds32(rb, 8 * 128 + sw_even), w3 = lds32(rb, 9 * 128 + sw_odd);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t sel = (uint32_t)b | ((uint32_t)b << 4) | ((uint32_t)(4 + b) << 8) | ((uint32_t)(4 + b) << 12);
+          const uint32_t p01 = __byte_perm(w0, w1, sel), p23 = __byte_perm(w2, w3, sel);
+          // nibble 2b (low) and 2b+1 (high) of rows (k0,k1) and (k2,k3)
+          uint32_t a0 = (p01 & LO) | MAGIC, a1 = ((p01 >> 4) & LO) | MAGIC;
+          uint32_t a2 = (p23 & LO) | MAGIC, a3 = ((p23 >> 4) & LO) | MAGIC;
+          a0 = mul2<BF16>(sub2<BF16>(a0, zm2[2 * b]), sc2[2 * b]);
+          a2 = mul2<BF16>(sub2<BF16>(a2, zm2[2 * b]), sc2[2 * b]);
+          a1 = mul2<BF16>(sub2<BF16>(a1, zm2[2 * b + 1]), sc2[2 * b + 1]);
+          a3 = mul2<BF16>(sub2<BF16>(a3, zm2[2 * b + 1]), sc2[2 * b + 1]);
+          tmem_st_16x128b_x2(acol + ((uint32_t)(16 * (b & 1)) << 16) + 64 * (b >> 1) + 8 * ks, a0, a1, a2, a3);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(smem_u32(&bar_afull[sa])); mbar_arrive(smem_u32(&bar_empty[s])); }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
+    const int g = lane & 7, r = (lane >> 3) & 1, bb = lane >> 4;
+    int nloc[2];
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      const int j = 2 * (2 * blk + bb) + r;
+      nloc[blk] = 64 * q + 8 * g + ((j < 4) ? 2 * j : 2 * (j - 4) + 1);
+    }
+    int lt = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++lt) {
+      const int tile_n = t / p.ntiles_t, tile_t = t % p.ntiles_t;
+      if (!wait_bar(&bar_dfull, lt & 1, s_abort, status)) break;
+      tc_fence_after();
+      const int tok0 = tile_t * kTileT;
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        const int n = tile_n * kTileN + nloc[blk];
+        const bool n_ok = n < p.N;
+        const float bv = (p.bias && n_ok) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
+        for (int c0 = 0; c0 < p.nt; c0 += 16) {
+          uint32_t d[16];
+          tmem_ld_32x32b_x16(lane_base + kColD + 128 * blk + c0, d);
+          tc_wait_ld();
+          if (n_ok) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int tok = tok0 + c0 + c;
+              if (tok < p.M) p.out[(size_t)tok * p.N + n] = float_to_raw16<BF16>(__uint_as_float(d[c]) + bv);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_dempty));
+    }
+  }
+
+  // all roles meet here, also after a give-up, so that tensor memory is always released
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
+}
+
+template <bool BF16>
+static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx,
+                    const Params& sp, int ctas, cudaStream_t st) {
+  static bool configured = false;  // idempotent attribute; a repeated set from two threads is harmless
+  if (!configured) {
+    if (cudaFuncSetAttribute(umma_prefill_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+      cudaGetLastError();
+      return NQB200_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  umma_prefill_kernel<BF16><<<ctas, kThreads, kSmem, st>>>(tw, ts, tz, tx, sp);
+  return check_launch();
+}
+
+}  // namespace pre
+
+bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
+  return M > 16 && g == 128 && K % 128 == 0 && N % 32 == 0;
+}
+
+int launch_umma_prefill(const GemmArgs& a) {
+  using namespace pre;
+  const int G = a.K / 128;
+  Params sp;
+  sp.bias = a.bias; sp.bias_dtype = a.bias_dtype; sp.out = (uint16_t*)a.out;
+  sp.M = a.M; sp.N = a.N; sp.G = G;
+  sp.ntiles_n = (a.N + kTileN - 1) / kTileN;
+  sp.ntiles_t = (a.M + kTileT - 1) / kTileT;
+  sp.nt = a.M >= kTileT ? kTileT : ((a.M + 15) / 16) * 16;
+  sp.status = (a.ws && a.ws_bytes >= (size_t)kCounterBytes) ? (int*)a.ws + (kCounterBytes / 4 - 1) : nullptr;
+  const long long tiles = (long long)sp.ntiles_n * sp.ntiles_t;
+  const int ctas = (int)(tiles < kNumSMs ? tiles : kNumSMs);
+  alignas(64) CUtensorMap tw, ts, tz, tx;
+  const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, G, a.N / 2, 1, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, G, a.N / 8, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && encode_2d(&tx, xdt, 2, a.x, a.M, a.K, kTileT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return NQB200_ERR_LAUNCH;
+  return a.dtype == NQB200_BF16 ? launch_t<true>(tw, ts, tz, tx, sp, ctas, a.stream)
+                                : launch_t<false>(tw, ts, tz, tx, sp, ctas, a.stream);
+}
+
+}  // namespace nqb200
