@@ -128,13 +128,30 @@ def shard_shape(K, N, kind, world):
 def make_layer(K, N, seed, dev, dtype):
     """A WQLinear_GEMM filled on the device with the benchmark's distributions."""
     import nanoquantization_b200 as nq
+    lin = nq.WQLinear_GEMM(4, GROUP, K, N, dev, False, dtype)
+    fill_layer(lin, seed, dev, dtype)
+    return lin
+
+
+def fill_layer(lin, seed, dev, dtype):
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
-    lin = nq.WQLinear_GEMM(4, GROUP, K, N, dev, False, dtype)
+    K, N = lin.in_features, lin.out_features
     # uniform 32-bit words = uniform nibbles, i.e. int4 weights / zero-points uniform in [0, 15]
     lin.qweight.copy_(torch.randint(-2 ** 31, 2 ** 31, (K, N // 8), generator=g, device=dev, dtype=torch.int64).to(torch.int32))
     lin.qzeros.copy_(torch.randint(-2 ** 31, 2 ** 31, (K // GROUP, N // 8), generator=g, device=dev, dtype=torch.int64).to(torch.int32))
     lin.qscales.copy_((torch.rand(K // GROUP, N, generator=g, device=dev) * 9e-3 + 1e-3).to(dtype))
+
+
+def make_tp_layer(K, N, kind, world, rank, seed, dev, dtype):
+    """The rank's shard of a (K, N) layer as the tensor-parallel class that an engine would use;
+    the shard is filled directly (random init) instead of being sliced from a full tensor."""
+    import nanoquantization_b200 as nq
+    if kind == "column":
+        lin = nq.ColumnParallelWQLinear(4, GROUP, K, N, world, rank, dev, False, dtype)
+    else:
+        lin = nq.RowParallelWQLinear(4, GROUP, K, N, world, rank, dev, False, dtype)
+    fill_layer(lin.shard, seed, dev, dtype)
     return lin
 
 
@@ -162,7 +179,10 @@ def run_ours(args):
     for si, (K, N, kind) in enumerate(SHAPES):
         k, n = shard_shape(K, N, kind, world)
         ncopy = max(2, -(-int(1.5 * L2_BYTES) // weight_bytes(k, n)))
-        layers[si] = [make_layer(k, n, 1000 * si + c + 17 * rank, dev, dtype) for c in range(ncopy)]
+        if world == 1:
+            layers[si] = [make_layer(k, n, 1000 * si + c, dev, dtype) for c in range(ncopy)]
+        else:
+            layers[si] = [make_tp_layer(K, N, kind, world, rank, 1000 * si + c + 17 * rank, dev, dtype) for c in range(ncopy)]
         for M in MS:
             g = torch.Generator(device="cpu"); g.manual_seed(M * 31 + si)
             xh = torch.randn(M, k, generator=g).to(dtype).pin_memory()
@@ -172,11 +192,7 @@ def run_ours(args):
     points = [(si, M) for M in MS for si in range(len(SHAPES))]  # M-major: a shape's reuses are far apart
 
     def call(si, M, copy, x):
-        lin = layers[si][copy % len(layers[si])]
-        y = lin(x)
-        if world > 1 and SHAPES[si][2] == "row":
-            dist.all_reduce(y)
-        return y
+        return layers[si][copy % len(layers[si])](x)  # row-parallel layers all-reduce inside
 
     # point j of a shape uses weight copy j, so a copy is reused only after the rest of the sweep
     # (>1 GB of other weights) has gone through L2

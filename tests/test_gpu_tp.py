@@ -1,0 +1,59 @@
+"""The tensor-parallel classes over NCCL on real GPUs (needs at least two)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    import nanoquantization_b200 as nq
+    from oracle import awq_oracle as O
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        errs = []
+        for (K, N, M) in ((1024, 512, 3), (1024, 512, 200)):
+            g = 128
+            c = O.make_case(K, N, M, group_size=g, dtype=torch.float16, seed=5, bias=True)
+            full = O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"], c["bias"])
+            col = nq.ColumnParallelWQLinear(4, g, K, N, world, rank, dev, True, torch.float16, gather_output=True)
+            col.load_full(c["qweight"].to(dev), c["qscales"].to(dev), c["qzeros"].to(dev), c["bias"].to(dev))
+            errs.append(O.rel_err(col(c["x"].to(dev)), full))
+            row = nq.RowParallelWQLinear(4, g, K, N, world, rank, dev, True, torch.float16)
+            row.load_full(c["qweight"].to(dev), c["qscales"].to(dev), c["qzeros"].to(dev), c["bias"].to(dev))
+            errs.append(O.rel_err(row(row.input_slice(c["x"].to(dev)).contiguous()), full))
+        torch.cuda.synchronize()
+        out.put((rank, errs))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_classes_world2_nccl():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, errs in res:
+        # same tolerance as the single-GPU parity tests; the row-parallel sum adds one fp16 rounding per rank
+        assert max(errs) <= 2e-3, (rank, errs)
