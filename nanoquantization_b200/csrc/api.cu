@@ -46,7 +46,7 @@ static int check_shape(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
 
 extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
-  if (umma_prefill_supports(M, N, K, g)) return (size_t)kCounterBytes;  // only the status word is used
+  if (umma_prefill_supports(M, N, K, g)) return umma_prefill_workspace_bytes(M, N, K);
   if (use_umma_decode(M, N, K, g)) return umma_decode_workspace_bytes(M, N, K);
   if (stream_supports(M, N, K, g)) return stream_workspace_bytes(M, N, K);
   if (!decode_mma_supports(M, N, K, g)) return 0;

@@ -52,6 +52,8 @@ constexpr int kColA = 0, kColD = 256, kTmemCols = 512;
 struct Params {
   const void* bias; int bias_dtype; uint16_t* out;
   int M, N, G, ntiles_n, ntiles_t, nt;  // nt: MMA N (tokens per tile rounded up to 16)
+  int ksplit;                           // CTAs along K per output tile (1: results go straight to `out`)
+  float* partials;                      // [ksplit][M][N] fp32 when ksplit > 1
   int* status;                          // may be null
 };
 
@@ -85,6 +87,19 @@ template <bool BF16> __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32
   return r;
 }
 
+// Work item w = (output tile, K split): token tile fastest, then K split, then column tile.
+struct Item { int tile_n, tile_t, ks, g0, g1; };
+__device__ __forceinline__ Item decode_item(int w, const Params& p) {
+  Item it;
+  it.tile_t = w % p.ntiles_t;
+  const int r = w / p.ntiles_t;
+  it.ks = r % p.ksplit;
+  it.tile_n = r / p.ksplit;
+  it.g0 = (it.ks * p.G) / p.ksplit;
+  it.g1 = ((it.ks + 1) * p.G) / p.ksplit;
+  return it;
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
@@ -103,8 +118,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int G = p.G;
-  const int ntiles = p.ntiles_n * p.ntiles_t;
+  const int nitems = p.ntiles_n * p.ntiles_t * p.ksplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kDequantWarps / 2 + 1); }
@@ -121,11 +135,9 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  // Units are numbered consecutively over this CTA's tiles: unit i belongs to local tile i / G.
-  // Tile t (global) = blockIdx.x + j * gridDim.x; token tile index varies fastest.
-  int my_tiles = 0;
-  for (int t = blockIdx.x; t < ntiles; t += gridDim.x) ++my_tiles;
-  const int nunits = my_tiles * G;
+  // Units (one group of one work item) are numbered consecutively over this CTA's items.
+  int nunits = 0;
+  for (int w = blockIdx.x; w < nitems; w += gridDim.x) { const Item it = decode_item(w, p); nunits += it.g1 - it.g0; }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -133,9 +145,10 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z); prefetch_tmap(&tm_x);
       int issued = 0, i = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-        const int tile_n = t / p.ntiles_t, tile_t = t % p.ntiles_t;
-        for (int grp = 0; grp < G; ++grp, ++i) {
+      for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x) {
+        const Item it = decode_item(w, p);
+        const int tile_n = it.tile_n, tile_t = it.tile_t;
+        for (int grp = it.g0; grp < it.g1; ++grp, ++i) {
           const int s = i % kStages;
           if (i >= kStages && !wait_bar(&bar_empty[s], ((i / kStages) - 1) & 1, s_abort, status)) { ok = false; break; }
           const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
@@ -156,26 +169,29 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BF16 ? 1 : 0, 128, p.nt);
+      int i = 0, li = 0;
       bool ok = true;
-      for (int i = 0; i < nunits && ok; ++i) {
-        const int s = i % kStages, sa = i % kAStages;
-        const int grp = i % G, lt = i / G;
-        if (grp == 0 && lt > 0 && !wait_bar(&bar_dempty, (lt - 1) & 1, s_abort, status)) break;  // epilogue drained D
-        if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) break;
-        if (!wait_bar(&bar_afull[sa], (i / kAStages) & 1, s_abort, status)) break;
-        tc_fence_after();
-        const uint32_t xaddr = smem_base + s * kStageBytes + kOffX0;
-        const uint32_t a0 = tmem + kColA + sa * 128, a1 = a0 + 64, d = tmem + kColD;
+      for (int w = blockIdx.x; w < nitems && ok; w += gridDim.x, ++li) {
+        const Item it = decode_item(w, p);
+        for (int grp = it.g0; grp < it.g1; ++grp, ++i) {
+          const int s = i % kStages, sa = i % kAStages;
+          if (grp == it.g0 && li > 0 && !wait_bar(&bar_dempty, (li - 1) & 1, s_abort, status)) { ok = false; break; }  // epilogue drained D
+          if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) { ok = false; break; }
+          if (!wait_bar(&bar_afull[sa], (i / kAStages) & 1, s_abort, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t xaddr = smem_base + s * kStageBytes + kOffX0;
+          const uint32_t a0 = tmem + kColA + sa * 128, a1 = a0 + 64, d = tmem + kColD;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bdesc = umma_smem_desc_sw128(xaddr + (ks >> 2) * 16384 + (ks & 3) * 32);
-          const uint32_t acc = (grp > 0 || ks > 0) ? 1u : 0u;
-          umma_ts(d, a0 + ks * 8, bdesc, idesc, acc);
-          umma_ts(d + 128, a1 + ks * 8, bdesc, idesc, acc);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t bdesc = umma_smem_desc_sw128(xaddr + (ks >> 2) * 16384 + (ks & 3) * 32);
+            const uint32_t acc = (grp > it.g0 || ks > 0) ? 1u : 0u;
+            umma_ts(d, a0 + ks * 8, bdesc, idesc, acc);
+            umma_ts(d + 128, a1 + ks * 8, bdesc, idesc, acc);
+          }
+          umma_commit(smem_u32(&bar_aempty[sa]));
+          umma_commit(smem_u32(&bar_empty[s]));
+          if (grp == it.g1 - 1) umma_commit(smem_u32(&bar_dfull));
         }
-        umma_commit(smem_u32(&bar_aempty[sa]));
-        umma_commit(smem_u32(&bar_empty[s]));
-        if (grp == G - 1) umma_commit(smem_u32(&bar_dfull));
       }
       // everything issued has completed before tensor memory may be released
       umma_commit(smem_u32(&bar_drain));
@@ -250,26 +266,35 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       nloc[blk] = 64 * q + 8 * g + ((j < 4) ? 2 * j : 2 * (j - 4) + 1);
     }
     int lt = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++lt) {
-      const int tile_n = t / p.ntiles_t, tile_t = t % p.ntiles_t;
+    for (int w = blockIdx.x; w < nitems; w += gridDim.x, ++lt) {
+      const Item it = decode_item(w, p);
+      const int tile_n = it.tile_n, tile_t = it.tile_t;
       if (!wait_bar(&bar_dfull, lt & 1, s_abort, status)) break;
       tc_fence_after();
       const int tok0 = tile_t * kTileT;
+      float* part = p.ksplit > 1 ? p.partials + (size_t)it.ks * p.M * p.N : nullptr;
 #pragma unroll
       for (int blk = 0; blk < 2; ++blk) {
         const int n = tile_n * kTileN + nloc[blk];
         const bool n_ok = n < p.N;
-        const float bv = (p.bias && n_ok) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
+        const float bv = (p.bias && n_ok && !part) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
         for (int c0 = 0; c0 < p.nt; c0 += 16) {
           uint32_t d[16];
           tmem_ld_32x32b_x16(lane_base + kColD + 128 * blk + c0, d);
           tc_wait_ld();
-          if (n_ok) {
+          if (!n_ok) continue;
+          const int tok = tok0 + c0;
+          const int ntok = min(16, p.M - tok);  // <= 0 when the whole batch of columns is beyond M
+          if (part) {
+            float* dst = part + (size_t)tok * p.N + n;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int tok = tok0 + c0 + c;
-              if (tok < p.M) p.out[(size_t)tok * p.N + n] = float_to_raw16<BF16>(__uint_as_float(d[c]) + bv);
-            }
+            for (int c = 0; c < 16; ++c)
+              if (c < ntok) __stcg(dst + (size_t)c * p.N, __uint_as_float(d[c]));
+          } else {
+            uint16_t* dst = p.out + (size_t)tok * p.N + n;
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if (c < ntok) dst[(size_t)c * p.N] = float_to_raw16<BF16>(__uint_as_float(d[c]) + bv);
           }
         }
       }
@@ -285,6 +310,28 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, kTmemCols); }
 }
 
+// out[m, n] = 16-bit( sum over the K splits, in split order, + bias ): 4 columns per thread.
+template <bool BF16>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partials, const void* bias, int bias_dtype,
+                                                            uint16_t* __restrict__ out, int M, int N, int ksplit) {
+  const size_t total4 = (size_t)M * N / 4;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int ks = 0; ks < ksplit; ++ks) {
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(partials + (size_t)ks * M * N) + i);
+      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    if (bias) {
+      const int n = (int)((i * 4) % N);
+      v.x += bias_to_float(bias, bias_dtype, n); v.y += bias_to_float(bias, bias_dtype, n + 1);
+      v.z += bias_to_float(bias, bias_dtype, n + 2); v.w += bias_to_float(bias, bias_dtype, n + 3);
+    }
+    const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
+    const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
+    reinterpret_cast<uint2*>(out)[i] = make_uint2(o0, o1);
+  }
+}
+
 template <bool BF16>
 static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx,
                     const Params& sp, int ctas, cudaStream_t st) {
@@ -297,6 +344,12 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
     configured = true;
   }
   umma_prefill_kernel<BF16><<<ctas, kThreads, kSmem, st>>>(tw, ts, tz, tx, sp);
+  if (check_launch() != NQB200_OK) return NQB200_ERR_LAUNCH;
+  if (sp.ksplit > 1) {
+    const size_t total4 = (size_t)sp.M * sp.N / 4;
+    const int blocks = (int)((total4 + 255) / 256 < (size_t)kNumSMs * 8 ? (total4 + 255) / 256 : (size_t)kNumSMs * 8);
+    splitk_reduce_kernel<BF16><<<blocks, 256, 0, st>>>(sp.partials, sp.bias, sp.bias_dtype, sp.out, sp.M, sp.N, sp.ksplit);
+  }
   return check_launch();
 }
 
@@ -304,6 +357,21 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
 
 bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   return M > 16 && g == 128 && K % 128 == 0 && N % 32 == 0;
+}
+
+// K is split across CTAs when the output tiles alone would leave most SMs idle.
+static int prefill_ksplit(int64_t M, int64_t N, int64_t K) {
+  const long long tiles = ((N + pre::kTileN - 1) / pre::kTileN) * ((M + pre::kTileT - 1) / pre::kTileT);
+  const int G = (int)(K / 128);
+  if (tiles * 2 > kNumSMs) return 1;
+  long long ks = kNumSMs / tiles;
+  if (ks > G) ks = G;
+  return (int)(ks < 1 ? 1 : ks);
+}
+
+size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  const int ks = prefill_ksplit(M, N, K);
+  return (size_t)kCounterBytes + (ks > 1 ? (size_t)ks * M * N * sizeof(float) : 0);
 }
 
 int launch_umma_prefill(const GemmArgs& a) {
@@ -316,7 +384,14 @@ int launch_umma_prefill(const GemmArgs& a) {
   sp.ntiles_t = (a.M + kTileT - 1) / kTileT;
   sp.nt = a.M >= kTileT ? kTileT : ((a.M + 15) / 16) * 16;
   sp.status = (a.ws && a.ws_bytes >= (size_t)kCounterBytes) ? (int*)a.ws + (kCounterBytes / 4 - 1) : nullptr;
-  const long long tiles = (long long)sp.ntiles_n * sp.ntiles_t;
+  sp.ksplit = prefill_ksplit(a.M, a.N, a.K);
+  sp.partials = nullptr;
+  if (sp.ksplit > 1) {
+    if (!a.ws || a.ws_bytes < umma_prefill_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
+    if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
+    sp.partials = (float*)((char*)a.ws + kCounterBytes);
+  }
+  const long long tiles = (long long)sp.ntiles_n * sp.ntiles_t * sp.ksplit;
   const int ctas = (int)(tiles < kNumSMs ? tiles : kNumSMs);
   alignas(64) CUtensorMap tw, ts, tz, tx;
   const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
