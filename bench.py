@@ -169,6 +169,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner out of stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     dtype = torch.float16
     lib = _lib.load()
@@ -240,8 +242,14 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    use_graph = world == 1  # NCCL calls stay outside graphs here
-    sweep_graph = capture(sweep_device) if use_graph else None
+    use_graph = True
+    try:
+        sweep_graph = capture(sweep_device)  # with tensor parallelism the NCCL all-reduces are captured too
+    except RuntimeError:
+        if world == 1:
+            raise
+        use_graph, sweep_graph = False, None  # plain launches if this NCCL build refuses capture
+        torch.cuda.synchronize()
     run_sweep = (lambda s: sweep_graph.replay()) if use_graph else sweep_device
     for w in range(max(args.warmup, 3)):
         run_sweep(w)
@@ -311,7 +319,7 @@ def run_ours(args):
             "config": {"workload": "w4a16_gemm_sweep g128 M{1,4,16,128,1024,4096} x 5 (K,N) shapes (config 2)",
                        "points_per_step": len(points), "parallelism": f"tp{world}",
                        "l2": "weights rotate over copies totalling >1.5x L2 per shape",
-                       "launch": "device-timed sweep replayed as one CUDA graph; e2e through WQLinear_GEMM.forward"},
+                       "launch": ("device-timed sweep replayed as one CUDA graph" if use_graph else "plain launches") + "; e2e through WQLinear_GEMM.forward"},
             "e2e": {"value": round(ms_e2e * 1e3 / args.steps, 2), "unit": "us", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": len(points) * args.steps,

@@ -106,7 +106,8 @@ int nqb200_gemm_decode_noalloc(const void* x, const void* qweight, const void* q
 int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Name of the kernel family nqb200_gemm would pick for this problem
- * ("decode_stream", "decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
+ * ("decode_stream", "decode_tcgen05", "decode_mma", "prefill_tcgen05", "prefill_tcgen05_pair",
+ * "generic"); for logs and tests. */
 const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
 
 #ifdef __cplusplus

@@ -42,7 +42,7 @@ namespace pre {
 
 constexpr int kTileN = 256, kTileT = 128, kUnitK = 128;
 constexpr int kStages = 4, kAStages = 2;
-constexpr int kDequantWarps = 16, kEpiWarps = 4;
+constexpr int kDequantWarps = 16, kEpiWarps = 12;  // three epilogue warps per lane quarter share a tile's token columns
 constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;
 constexpr int kOffW = 0, kOffX0 = 16384, kOffX1 = 32768, kOffSc = 49152, kOffZ = 49664, kStageBytes = 50176;
 constexpr int kSmem = kStages * kStageBytes + 1024;
@@ -57,12 +57,15 @@ struct Params {
   int* status;                          // may be null
 };
 
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+// `sleep_ns` > 0: back off between polls (roles that wait long should not take issue slots).
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                         unsigned sleep_ns = 0) {
   const uint32_t b = smem_u32(bar);
   if (mbar_try_wait(b, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(b, parity)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((i & 63u) == 0) {
       if (*abort_flag) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) {
@@ -256,7 +259,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;
+    const int q = warp & 3, sub = (warp - 2 - kDequantWarps) >> 2;
     const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
     const int g = lane & 7, r = (lane >> 3) & 1, bb = lane >> 4;
     int nloc[2];
@@ -269,7 +272,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int w = blockIdx.x; w < nitems; w += gridDim.x, ++lt) {
       const Item it = decode_item(w, p);
       const int tile_n = it.tile_n, tile_t = it.tile_t;
-      if (!wait_bar(&bar_dfull, lt & 1, s_abort, status)) break;
+      if (!wait_bar(&bar_dfull, lt & 1, s_abort, status, 200)) break;
       tc_fence_after();
       const int tok0 = tile_t * kTileT;
       float* part = p.ksplit > 1 ? p.partials + (size_t)it.ks * p.M * p.N : nullptr;
@@ -278,7 +281,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int n = tile_n * kTileN + nloc[blk];
         const bool n_ok = n < p.N;
         const float bv = (p.bias && n_ok && !part) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
-        for (int c0 = 0; c0 < p.nt; c0 += 16) {
+        for (int c0 = 16 * sub; c0 < p.nt; c0 += 16 * (kEpiWarps / 4)) {
           uint32_t d[16];
           tmem_ld_32x32b_x16(lane_base + kColD + 128 * blk + c0, d);
           tc_wait_ld();
