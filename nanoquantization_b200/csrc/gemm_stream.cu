@@ -11,11 +11,13 @@
 //                   zero-points, two boxes of activations), completion on an
 //                   mbarrier.  About 190 KB per SM is in flight from the
 //                   first cycle, which is what keeps HBM busy at these sizes.
+//   sum(x) warp   : sum over the group's 128 k of every token, once per unit, into
+//                   the stage (the tensor pipe is this kernel's scarce resource, so
+//                   this is not done with an all-ones mma).
 //   8 consumer warps : warp w owns columns 64w..64w+63 of the tile for the whole
-//                   group; arithmetic exactly as in the register-fed kernel
-//                   (raw nibbles as fp16 subnormals into mma.sync m16n8k16,
-//                   one extra all-ones mma for sum(x), scale and zero-point
-//                   applied once per group in fp32).  The 128-byte swizzle and
+//                   group; arithmetic as in the register-fed kernel (raw nibbles
+//                   as fp16 subnormals into mma.sync m16n8k16, scale and
+//                   zero-point applied once per group in fp32).  The 128-byte swizzle and
 //                   the mma's own k order (2t, 2t+1, 2t+8, 2t+9) make every
 //                   shared-memory load conflict-free.
 //
@@ -34,7 +36,7 @@ namespace nqb200 {
 
 constexpr int kUnitN = 512, kUnitK = 128;
 constexpr int kConsumerWarps = 8;
-constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
+constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;  // consumers, TMA producer, sum(x) warp
 constexpr int kOffW0 = 0, kOffW1 = 16384, kOffX0 = 32768;
 
 // Up to 8 tokens (MT = 1): two CTAs per SM with three stages each, so that 16 consumer warps
@@ -46,7 +48,8 @@ template <int MT> struct StreamCfg {
   static constexpr int kOffX1 = kOffX0 + kXBox;
   static constexpr int kOffSc = kOffX0 + 2 * kXBox;
   static constexpr int kOffZ = kOffSc + 1024;
-  static constexpr int kStageBytes = (kOffZ + 256 + 1023) / 1024 * 1024;
+  static constexpr int kOffXs = kOffZ + 256;                  // sum over the group's k of each token, fp32
+  static constexpr int kStageBytes = (kOffXs + 64 + 1023) / 1024 * 1024;
   static constexpr int kSmem = kStages * kStageBytes + 1024;
   static constexpr int kSlotFloats = 8 * MT * kUnitN;
   static constexpr uint32_t kStageTx = 2 * 16384 + 2 * kXBox + 1024 + 256;
@@ -99,15 +102,14 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
               const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x,
               const StreamParams p) {
   constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
-  constexpr uint32_t ONES = BF16 ? 0x3F803F80u : 0x3C003C00u;
   constexpr float MULT_LO = BF16 ? 1.f : 16777216.f, MULT_HI = BF16 ? 1.f : 1048576.f, OFF = BF16 ? 128.f : 0.f;
   using Cfg = StreamCfg<MT>;
   constexpr int kStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kOffX1 = Cfg::kOffX1, kOffSc = Cfg::kOffSc,
-                kOffZ = Cfg::kOffZ, kSlotFloats = Cfg::kSlotFloats;
+                kOffZ = Cfg::kOffZ, kOffXs = Cfg::kOffXs, kSlotFloats = Cfg::kSlotFloats;
   constexpr uint32_t kStageTx = Cfg::kStageTx;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_seg;
+  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_xs[kStages], bar_seg;
   __shared__ int s_last;
   __shared__ int s_slot[2 * kNumSMs];  // slot of each contributor of the tile being finalised
 
@@ -120,7 +122,9 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   const int G = p.G;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kConsumerWarps); }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kConsumerWarps); mbar_init(smem_u32(&bar_xs[s]), 1);
+    }
     mbar_init(smem_u32(&bar_seg), kConsumerWarps);
     mbar_fence_init();
   }
@@ -151,6 +155,31 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       // do not leave while a copy of ours may still be landing in this CTA's shared memory
       for (int i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
         mbar_wait(smem_u32(&bar_full[i % kStages]), (i / kStages) & 1);
+    }
+    return;
+  }
+  if (warp == kConsumerWarps + 1) {
+    // ------------------------------------------------------------- sum(x) warp
+    // lane l adds k = 4l..4l+3 of a token's row (one 8-byte load from the swizzled tile), then a butterfly
+    const uint32_t ch = (uint32_t)(lane & 15) >> 1;
+    for (int i = 0; i < nunits; ++i) {
+      const int s = i % kStages;
+      if (!mbar_wait(smem_u32(&bar_full[s]), (i / kStages) & 1)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); break; }
+      uint8_t* st = const_cast<uint8_t*>(smem_gen) + s * kStageBytes;
+      const uint8_t* xb = st + ((lane >> 4) ? kOffX1 : kOffX0) + 8 * (lane & 1);
+      float mine = 0.f;
+#pragma unroll
+      for (int m = 0; m < 8 * MT; ++m) {
+        const uint2 v = *reinterpret_cast<const uint2*>(xb + m * 128 + ((ch ^ (uint32_t)(m & 7)) << 4));
+        float a = raw16_to_float<BF16>((uint16_t)(v.x & 0xFFFF)) + raw16_to_float<BF16>((uint16_t)(v.x >> 16)) +
+                  raw16_to_float<BF16>((uint16_t)(v.y & 0xFFFF)) + raw16_to_float<BF16>((uint16_t)(v.y >> 16));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+        if (lane == m) mine = a;
+      }
+      if (lane < 8 * MT) *reinterpret_cast<float*>(st + kOffXs + 4 * lane) = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_xs[s]));
     }
     return;
   }
@@ -189,11 +218,9 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     const uint8_t* st = smem_gen + s * kStageBytes;
     const uint8_t* wb = st + w_off + row0;
 
-    float acc[MT][4][4], xs[MT][4];
+    float acc[MT][4][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) xs[mt][q] = 0.f;
 #pragma unroll
       for (int b = 0; b < 4; ++b)
 #pragma unroll
@@ -227,12 +254,21 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) mma16816s<BF16>(acc[mt][b], a0, a1, a2, a3, xb0[mt], xb1[mt]);
       }
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) mma16816s<BF16>(xs[mt], ONES, ONES, ONES, ONES, xb0[mt], xb1[mt]);
     }
 
     // scale, power of two and zero-point, once per group
+    if (!mbar_wait(smem_u32(&bar_xs[s]), (i / kStages) & 1)) {
+      atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      alive = false;
+      break;
+    }
     {
+      float xs[MT][2];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const float2 v = *reinterpret_cast<const float2*>(st + kOffXs + 4 * (8 * mt + 2 * tig));
+        xs[mt][0] = v.x; xs[mt][1] = v.y;
+      }
       const uint4 sv = lds128(st, kOffSc + (uint32_t)(64 * w + 8 * gq) * 2);
       const uint32_t zw = lds32(st, kOffZ + (uint32_t)(8 * w + gq) * 4);
       const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};

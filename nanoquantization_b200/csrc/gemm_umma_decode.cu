@@ -11,9 +11,10 @@
 // One persistent CTA per SM; units of 128 rows (one group) x 256 columns are
 // dealt to CTAs as equal contiguous ranges of u = tile * G + group.
 //
-//   warp 0      TMA producer: packed weights (128 x 128 B, 128-byte swizzle),
-//               activations (two 16 x 64 boxes, 128-byte swizzle), the group's
-//               scales and zero-points, into an 8-stage ring.
+//   warp 0      TMA producer: packed weights (128 x 128 B, 128-byte swizzle) into an
+//               8-stage ring that the dequantisers release; activations (two
+//               16 x 64 boxes, 128-byte swizzle), scales and zero-points into a
+//               16-stage ring that lives until the group's epilogue.
 //   warps 2-9   dequantisers.  A packed word holds 8 columns of one k; PRMT
 //               interleaves byte b of rows k and k+1 and two ANDs leave the
 //               nibbles as fp16 subnormals (q * 2^-24, q * 2^-20), two adjacent
@@ -25,8 +26,8 @@
 //               the epilogue undoes).  No subtract, no multiply, no smem write.
 //   warp 1      issues the MMAs: per 16-row k-step one for each A block.  An MMA
 //               that accumulates onto the previous one waits for it (about 120
-//               cycles at this tiny N), so the 8 k-steps of a group rotate over
-//               4 accumulators per block and the epilogue adds the four.
+//               cycles at this tiny N), so the 8 k-steps of a group alternate over
+//               2 accumulators per block and the epilogue adds the two.
 //   warps 10-13 epilogue, once per group: sum_k x[tok, k] from the activation
 //               tile in shared memory, read D, then in fp32
 //               total += s * 2^(24|20) * D - s * z * sum(x).
@@ -44,13 +45,18 @@ namespace nqb200 {
 namespace dec {
 
 constexpr int kUnitN = 256, kUnitK = 128;
-constexpr int kStages = 8, kAStages = 2, kAcc = 4;
+constexpr int kWStages = 8, kXStages = 16, kAStages = 3, kAcc = 2;
 constexpr int kDequantWarps = 8, kEpiWarps = 4;
 constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;
-constexpr int kOffW = 0, kOffX0 = 16384, kOffX1 = 18432, kOffSc = 20480, kOffZ = 20992, kStageBytes = 21504;
-constexpr int kSmem = kStages * kStageBytes + 1024;
-constexpr uint32_t kStageTx = 16384 + 4096 + 512 + 128;
-constexpr int kColA = 0, kColD = 256, kDBuf = 2 * kAcc * 16, kTmemCols = 512;  // A: 2 x 128 columns, D: 2 x 128
+// two rings: the packed weights (released by the dequantisers as soon as they are in tensor memory)
+// and the small per-group data -- activations, scales, zero-points -- that the MMAs and the
+// epilogue still need much later
+constexpr int kWStageBytes = 16384;
+constexpr int kOffX0 = 0, kOffX1 = 2048, kOffSc = 4096, kOffZ = 4608, kXStageBytes = 5120;
+constexpr int kXRingBase = kWStages * kWStageBytes;
+constexpr int kSmem = kXRingBase + kXStages * kXStageBytes + 1024;
+constexpr uint32_t kWTx = 16384, kXTx = 4096 + 512 + 128;
+constexpr int kColA = 0, kColD = 384, kDBuf = 2 * kAcc * 16, kTmemCols = 512;  // A: 3 x 128 columns, D: 2 x 64
 constexpr int kSlotFloats = 16 * kUnitN;
 constexpr int kStatusWord = kCounterBytes / 4 - 1;
 
@@ -90,7 +96,8 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   constexpr float MULT_LO = BF16 ? 1.f : 16777216.f, MULT_HI = BF16 ? 1.f : 1048576.f, OFF = BF16 ? 128.f : 0.f;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_afull[kAStages], bar_aempty[kAStages],
+  __shared__ __align__(8) uint64_t bar_wfull[kWStages], bar_wempty[kWStages], bar_xfull[kXStages], bar_xempty[kXStages],
+      bar_afull[kAStages], bar_aempty[kAStages],
       bar_dfull[2], bar_dempty[2], bar_seg, bar_drain;
   __shared__ uint32_t s_tmem;
   __shared__ int s_last, s_abort_i;
@@ -107,7 +114,8 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const int G = p.G;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kDequantWarps + 1 + kEpiWarps); }
+    for (int s = 0; s < kWStages; ++s) { mbar_init(smem_u32(&bar_wfull[s]), 1); mbar_init(smem_u32(&bar_wempty[s]), kDequantWarps); }
+    for (int s = 0; s < kXStages; ++s) { mbar_init(smem_u32(&bar_xfull[s]), 1); mbar_init(smem_u32(&bar_xempty[s]), 1 + kEpiWarps); }
     for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&bar_afull[s]), kDequantWarps); mbar_init(smem_u32(&bar_aempty[s]), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(smem_u32(&bar_dfull[s]), 1); mbar_init(smem_u32(&bar_dempty[s]), kEpiWarps); }
     mbar_init(smem_u32(&bar_seg), kEpiWarps);
@@ -128,43 +136,48 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
       int issued = 0;
       for (int i = 0; i < nunits; ++i) {
-        const int s = i % kStages;
-        if (i >= kStages && !wait_bar(&bar_empty[s], ((i / kStages) - 1) & 1, s_abort, status)) break;
-        const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
-        mbar_expect_tx(bar, kStageTx);
-        tma_load_2d(st + kOffW, &tm_w, tile * 32, grp * kUnitK, bar);
-        tma_load_2d(st + kOffX0, &tm_x, grp * kUnitK, 0, bar);
-        tma_load_2d(st + kOffX1, &tm_x, grp * kUnitK + 64, 0, bar);
-        tma_load_2d(st + kOffSc, &tm_sc, tile * 128, grp, bar);
-        tma_load_2d(st + kOffZ, &tm_z, tile * 32, grp, bar);
+        const int ws = i % kWStages, xs = i % kXStages;
+        if (i >= kWStages && !wait_bar(&bar_wempty[ws], ((i / kWStages) - 1) & 1, s_abort, status)) break;
+        if (i >= kXStages && !wait_bar(&bar_xempty[xs], ((i / kXStages) - 1) & 1, s_abort, status)) break;
+        const uint32_t wst = smem_base + ws * kWStageBytes, xst = smem_base + kXRingBase + xs * kXStageBytes;
+        const uint32_t wbar = smem_u32(&bar_wfull[ws]), xbar = smem_u32(&bar_xfull[xs]);
+        mbar_expect_tx(wbar, kWTx);
+        tma_load_2d(wst, &tm_w, tile * 32, grp * kUnitK, wbar);
+        mbar_expect_tx(xbar, kXTx);
+        tma_load_2d(xst + kOffX0, &tm_x, grp * kUnitK, 0, xbar);
+        tma_load_2d(xst + kOffX1, &tm_x, grp * kUnitK + 64, 0, xbar);
+        tma_load_2d(xst + kOffSc, &tm_sc, tile * 128, grp, xbar);
+        tma_load_2d(xst + kOffZ, &tm_z, tile * 32, grp, xbar);
         ++issued;
         if (++grp == G) { grp = 0; ++tile; }
       }
       // do not leave while a copy of ours may still be landing in this CTA's shared memory
-      for (int i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
-        mbar_wait(smem_u32(&bar_full[i % kStages]), (i / kStages) & 1);
+      for (int i = issued > kWStages ? issued - kWStages : 0; i < issued; ++i)
+        mbar_wait(smem_u32(&bar_wfull[i % kWStages]), (i / kWStages) & 1);
+      for (int i = issued > kXStages ? issued - kXStages : 0; i < issued; ++i)
+        mbar_wait(smem_u32(&bar_xfull[i % kXStages]), (i / kXStages) & 1);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BF16 ? 1 : 0, 128, 16);
       for (int i = 0; i < nunits; ++i) {
-        const int s = i % kStages, sa = i % kAStages, sd = i & 1;
-        if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) break;
+        const int xs = i % kXStages, sa = i % kAStages, sd = i & 1;
+        if (!wait_bar(&bar_xfull[xs], (i / kXStages) & 1, s_abort, status)) break;
         if (!wait_bar(&bar_afull[sa], (i / kAStages) & 1, s_abort, status)) break;
         if (i >= 2 && !wait_bar(&bar_dempty[sd], ((i >> 1) - 1) & 1, s_abort, status)) break;
         tc_fence_after();
-        const uint32_t xaddr = smem_base + s * kStageBytes + kOffX0;
+        const uint32_t xaddr = smem_base + kXRingBase + xs * kXStageBytes + kOffX0;
         const uint32_t a0 = tmem + kColA + sa * 128, a1 = a0 + 64, d = tmem + kColD + sd * kDBuf;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t bdesc = umma_smem_desc_sw128(xaddr + (ks >> 2) * 2048 + (ks & 3) * 32);
-          umma_ts(d + 16 * (ks & 3), a0 + ks * 8, bdesc, idesc, ks >= kAcc);
-          umma_ts(d + 16 * kAcc + 16 * (ks & 3), a1 + ks * 8, bdesc, idesc, ks >= kAcc);
+          umma_ts(d + 16 * (ks % kAcc), a0 + ks * 8, bdesc, idesc, ks >= kAcc);
+          umma_ts(d + 16 * kAcc + 16 * (ks % kAcc), a1 + ks * 8, bdesc, idesc, ks >= kAcc);
         }
         umma_commit(smem_u32(&bar_aempty[sa]));
         umma_commit(smem_u32(&bar_dfull[sd]));
-        umma_commit(smem_u32(&bar_empty[s]));
+        umma_commit(smem_u32(&bar_xempty[xs]));
       }
       // everything issued has completed before tensor memory may be released
       umma_commit(smem_u32(&bar_drain));
@@ -180,11 +193,11 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t row0 = (uint32_t)(2 * tig) * 128;
     const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
     for (int i = 0; i < nunits; ++i) {
-      const int s = i % kStages, sa = i % kAStages;
-      if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) break;
+      const int ws = i % kWStages, sa = i % kAStages;
+      if (!wait_bar(&bar_wfull[ws], (i / kWStages) & 1, s_abort, status)) break;
       if (i >= kAStages && !wait_bar(&bar_aempty[sa], ((i / kAStages) - 1) & 1, s_abort, status)) break;
       tc_fence_after();
-      const uint8_t* wb = smem_gen + s * kStageBytes + kOffW + row0;
+      const uint8_t* wb = smem_gen + ws * kWStageBytes + row0;
       const uint32_t acol = lane_base + kColA + sa * 128;
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
@@ -209,7 +222,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(smem_u32(&bar_afull[sa])); mbar_arrive(smem_u32(&bar_empty[s])); }
+      if (lane == 0) { mbar_arrive(smem_u32(&bar_afull[sa])); mbar_arrive(smem_u32(&bar_wempty[ws])); }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -238,9 +251,9 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     uint32_t seg_phase = 0;
 
     for (int i = 0; i < nunits; ++i) {
-      const int s = i % kStages, sd = i & 1;
-      if (!wait_bar(&bar_full[s], (i / kStages) & 1, s_abort, status)) break;  // activations, scales, zero-points
-      const uint8_t* st = smem_gen + s * kStageBytes;
+      const int xq = i % kXStages, sd = i & 1;
+      if (!wait_bar(&bar_xfull[xq], (i / kXStages) & 1, s_abort, status)) break;  // activations, scales, zero-points
+      const uint8_t* st = smem_gen + kXRingBase + xq * kXStageBytes;
       // sum over the group's 128 k of each token: lane l adds k = 4l..4l+3, then a butterfly
       float xs[MC];
       {
@@ -276,7 +289,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         tc_wait_ld();
 #pragma unroll
         for (int m = 0; m < MC; ++m)
-          dsum[blk][m] = (__uint_as_float(da[0][m]) + __uint_as_float(da[1][m])) + (__uint_as_float(da[2][m]) + __uint_as_float(da[3][m]));
+          dsum[blk][m] = __uint_as_float(da[0][m]) + __uint_as_float(da[1][m]);
       }
       tc_fence_before();
       __syncwarp();
@@ -286,7 +299,7 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
         for (int m = 0; m < MC; ++m) total[blk][m] += cA[blk] * dsum[blk][m] - cB[blk] * xs[m];
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+      if (lane == 0) mbar_arrive(smem_u32(&bar_xempty[xq]));
 
       const bool tile_done = grp == G - 1;
       if (tile_done || i == nunits - 1) {
