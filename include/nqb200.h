@@ -98,6 +98,14 @@ int nqb200_gemm_decode_noalloc(const void* x, const void* qweight, const void* q
                                const void* bias, int bias_dtype, void* out,
                                int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype, void* stream);
 
+/* Quantise an nn.Linear weight [N, K] (weight_dtype: 0 f16, 1 bf16, 2 f32) group-wise to int4 with
+ * zero-points and pack it into qweight / qscales (scales_dtype) / qzeros, in one kernel.  Replaces,
+ * rounding for rounding, pseudo_quantize (nanoquantization/utils/quantization.py:20-41) followed by
+ * WQLinear_GEMM.from_linear (gemm.py:478-548), the pair the quantizer runs per layer
+ * (awq/quantizer.py:150-170). */
+int nqb200_quantize_pack(const void* weight, int weight_dtype, void* qweight, void* qscales, void* qzeros,
+                         int64_t N, int64_t K, int64_t group_size, int scales_dtype, void* stream);
+
 /* Waits for `stream`, then returns the status the kernels recorded in this
  * workspace: NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a bounded device-side wait
  * (an mbarrier or a tile counter) gave up; the record is cleared.  The kernels

@@ -1,0 +1,269 @@
+"""A small serving engine around the quantised model: paged KV cache, block
+manager, continuous-batching scheduler, model runner with CUDA-graph decode.
+
+The reference has none of this (its only execution is a full-sequence forward
+for a loss, models/qwen3_quantized.py:326-341); it exists so that the W4A16
+linears can be measured where they are used: prefill of batched prompts and
+greedy decode steps over a KV cache.  Attention is not the subject here and
+goes through PyTorch's scaled_dot_product_attention: per prompt at prefill,
+over the gathered pages of each sequence at decode.
+
+Layout: per layer two tensors ``[num_blocks, block_size, kv_heads, head_dim]``;
+a sequence owns a list of blocks; ``slot = block * block_size + offset``.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Sequence as Seq
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt: list[int]
+    max_new_tokens: int
+    output: list[int] = field(default_factory=list)
+    blocks: list[int] = field(default_factory=list)
+    prefilled: bool = False
+    carried: list[int] = field(default_factory=list)  # tokens generated before a preemption (now part of the prompt)
+
+    def __len__(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def finished(self) -> bool:
+        return len(self.output) >= self.max_new_tokens
+
+
+class BlockManager:
+    """Free-list allocator of KV-cache blocks."""
+
+    def __init__(self, num_blocks: int, block_size: int):
+        self.block_size = block_size
+        self.free = deque(range(num_blocks))
+
+    def blocks_needed(self, n_tokens: int) -> int:
+        return -(-n_tokens // self.block_size)
+
+    def can_allocate(self, n_tokens: int) -> bool:
+        return self.blocks_needed(n_tokens) <= len(self.free)
+
+    def ensure(self, seq: Sequence, n_tokens: int) -> bool:
+        """Grow ``seq`` to hold ``n_tokens``; False (and no change) if the pool is exhausted."""
+        need = self.blocks_needed(n_tokens) - len(seq.blocks)
+        if need > len(self.free):
+            return False
+        for _ in range(max(need, 0)):
+            seq.blocks.append(self.free.popleft())
+        return True
+
+    def release(self, seq: Sequence) -> None:
+        self.free.extend(seq.blocks)
+        seq.blocks = []
+
+
+class PagedKVCache:
+    def __init__(self, num_layers, num_blocks, block_size, kv_heads, head_dim, dtype, device):
+        shape = (num_blocks, block_size, kv_heads, head_dim)
+        self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self.block_size = block_size
+
+    def write(self, layer: int, slots: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        self.k[layer].view(-1, *k.shape[1:]).index_copy_(0, slots, k)
+        self.v[layer].view(-1, *v.shape[1:]).index_copy_(0, slots, v)
+
+
+class Scheduler:
+    """Prefill has priority: waiting prompts are admitted while blocks and the token budget last;
+    otherwise every running sequence decodes one token.  A sequence that cannot grow is preempted
+    (its blocks are released and it returns to the waiting queue to be prefilled again)."""
+
+    def __init__(self, blocks: BlockManager, max_batch: int, max_prefill_tokens: int):
+        self.blocks, self.max_batch, self.max_prefill_tokens = blocks, max_batch, max_prefill_tokens
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+
+    def add(self, seq: Sequence) -> None:
+        self.waiting.append(seq)
+
+    def step(self) -> tuple[str, list[Sequence]]:
+        batch, tokens = [], 0
+        while self.waiting and len(self.running) + len(batch) < self.max_batch:
+            s = self.waiting[0]
+            n = len(s)
+            if tokens + n > self.max_prefill_tokens and batch:
+                break
+            if not self.blocks.ensure(s, n + 1):
+                break
+            self.waiting.popleft()
+            batch.append(s)
+            tokens += n
+        if batch:
+            return "prefill", batch
+        ready = []
+        i = 0
+        while i < len(self.running):
+            s = self.running[i]
+            if self.blocks.ensure(s, len(s) + 1):
+                ready.append(s)
+                i += 1
+                continue
+            # no block left for s to grow into: preempt the youngest running sequence and try again
+            victim = self.running.pop()
+            self.blocks.release(victim)
+            if victim in ready:
+                ready.remove(victim)
+            victim.carried += victim.output
+            victim.max_new_tokens -= len(victim.output)
+            victim.prompt, victim.output, victim.prefilled = victim.prompt + victim.output, [], False
+            self.waiting.appendleft(victim)
+        return "decode", ready
+
+    def finish_step(self, kind: str, batch: list[Sequence]) -> list[Sequence]:
+        done = []
+        if kind == "prefill":
+            self.running.extend(batch)
+        for s in batch:
+            if s.finished:
+                done.append(s)
+                self.running.remove(s)
+                self.blocks.release(s)
+        return done
+
+
+class LLMEngine:
+    def __init__(self, model, num_blocks: int, block_size: int = 256, max_batch: int = 64,
+                 max_prefill_tokens: int = 16384, use_cuda_graph: bool = True):
+        self.model = model
+        attn = model.model.layers[0].self_attn
+        self.device = model.lm_head.weight.device
+        self.dtype = model.lm_head.weight.dtype
+        self.kv_heads, self.q_heads, self.head_dim = attn.num_kv_heads, attn.num_heads, attn.head_dim
+        self.block_size = block_size
+        self.cache = PagedKVCache(len(model.model.layers), num_blocks, block_size, self.kv_heads, self.head_dim,
+                                  self.dtype, self.device)
+        self.blocks = BlockManager(num_blocks, block_size)
+        self.scheduler = Scheduler(self.blocks, max_batch, max_prefill_tokens)
+        self.use_cuda_graph = use_cuda_graph
+        self._graphs: dict[tuple[int, int], tuple] = {}
+        self._next_id = 0
+
+    # ------------------------------------------------------------------ attention
+    def _prefill_attend(self, layer: int, slots: torch.Tensor, lens: list[int]) -> Callable:
+        def attend(q, k, v):
+            self.cache.write(layer, slots, k, v)
+            outs, o = [], 0
+            for n in lens:
+                qs, ks, vs = (t[o:o + n].transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+                outs.append(F.scaled_dot_product_attention(qs, ks, vs, is_causal=True,
+                                                           enable_gqa=self.q_heads != self.kv_heads)[0].transpose(0, 1))
+                o += n
+            return torch.cat(outs, dim=0)
+        return attend
+
+    def _decode_attend(self, layer: int, slots: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor,
+                       max_blocks: int) -> Callable:
+        def attend(q, k, v):
+            self.cache.write(layer, slots, k, v)
+            B = q.shape[0]
+            kk = self.cache.k[layer][block_tables[:, :max_blocks]].reshape(B, -1, self.kv_heads, self.head_dim)
+            vv = self.cache.v[layer][block_tables[:, :max_blocks]].reshape(B, -1, self.kv_heads, self.head_dim)
+            S = kk.shape[1]
+            mask = torch.arange(S, device=q.device)[None, :] < ctx_lens[:, None]          # [B, S]
+            o = F.scaled_dot_product_attention(q.unsqueeze(2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                               attn_mask=mask[:, None, None, :], enable_gqa=self.q_heads != self.kv_heads)
+            return o.squeeze(2)
+        return attend
+
+    # --------------------------------------------------------------------- steps
+    @torch.no_grad()
+    def _prefill(self, batch: list[Sequence]) -> torch.Tensor:
+        toks, pos, slots, lens = [], [], [], []
+        for s in batch:
+            n = len(s)
+            ids = s.prompt + s.output
+            toks += ids
+            pos += list(range(n))
+            slots += [s.blocks[i // self.block_size] * self.block_size + i % self.block_size for i in range(n)]
+            lens.append(n)
+        dev = self.device
+        toks_t = torch.tensor(toks, dtype=torch.long, device=dev)
+        pos_t = torch.tensor(pos, dtype=torch.long, device=dev)
+        slots_t = torch.tensor(slots, dtype=torch.long, device=dev)
+        h = self.model.model.forward_tokens(toks_t, pos_t, lambda i: self._prefill_attend(i, slots_t, lens))
+        last = torch.tensor([sum(lens[:i + 1]) - 1 for i in range(len(lens))], dtype=torch.long, device=dev)
+        return self.model.greedy_tokens(h[last])
+
+    def _decode_inputs(self, batch: list[Sequence], max_blocks: int):
+        B = len(batch)
+        toks = torch.tensor([(s.output or s.prompt)[-1] for s in batch], dtype=torch.long)
+        pos = torch.tensor([len(s) - 1 for s in batch], dtype=torch.long)
+        slots = torch.tensor([s.blocks[(len(s) - 1) // self.block_size] * self.block_size + (len(s) - 1) % self.block_size
+                              for s in batch], dtype=torch.long)
+        bt = torch.zeros(B, max_blocks, dtype=torch.long)
+        for i, s in enumerate(batch):
+            bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.long)
+        ctx = torch.tensor([len(s) for s in batch], dtype=torch.long)
+        return toks, pos, slots, bt, ctx
+
+    def _decode_forward(self, toks, pos, slots, bt, ctx, max_blocks):
+        h = self.model.model.forward_tokens(toks, pos, lambda i: self._decode_attend(i, slots, bt, ctx, max_blocks))
+        return self.model.greedy_tokens(h)
+
+    @torch.no_grad()
+    def _decode(self, batch: list[Sequence]) -> torch.Tensor:
+        B = len(batch)
+        max_blocks = max(len(s.blocks) for s in batch)
+        host = self._decode_inputs(batch, max_blocks)
+        if not self.use_cuda_graph:
+            return self._decode_forward(*(t.to(self.device) for t in host), max_blocks)
+        key = (B, max_blocks)
+        if key not in self._graphs:
+            static = [t.to(self.device) for t in host]
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._decode_forward(*static, max_blocks)      # warm up outside the capture
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._decode_forward(*static, max_blocks)
+            self._graphs[key] = (graph, static, out)
+        graph, static, out = self._graphs[key]
+        for dst, src in zip(static, host):
+            dst.copy_(src, non_blocking=True)
+        graph.replay()
+        return out
+
+    # ----------------------------------------------------------------------- API
+    def add_request(self, prompt: Seq[int], max_new_tokens: int) -> int:
+        sid = self._next_id
+        self._next_id += 1
+        self.scheduler.add(Sequence(sid, list(prompt), max_new_tokens))
+        return sid
+
+    def step(self) -> list[Sequence]:
+        kind, batch = self.scheduler.step()
+        if not batch:
+            return []
+        new = (self._prefill(batch) if kind == "prefill" else self._decode(batch)).tolist()
+        for s, t in zip(batch, new):
+            s.output.append(int(t))
+            s.prefilled = True
+        return self.scheduler.finish_step(kind, batch)
+
+    def generate(self, prompts: Seq[Seq[int]], max_new_tokens) -> list[list[int]]:
+        if isinstance(max_new_tokens, int):
+            max_new_tokens = [max_new_tokens] * len(prompts)
+        ids = [self.add_request(p, n) for p, n in zip(prompts, max_new_tokens)]
+        results: dict[int, list[int]] = {}
+        while self.scheduler.waiting or self.scheduler.running:
+            for s in self.step():
+                results[s.seq_id] = s.carried + s.output
+        return [results[i] for i in ids]

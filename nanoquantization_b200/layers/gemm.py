@@ -236,6 +236,33 @@ class WQLinear_GEMM(nn.Module):
         awq_linear.qzeros = pack_int4(zeros.to(torch.int32))
         return awq_linear
 
+    @classmethod
+    def from_float(cls, linear_layer: nn.Linear, w_bits: int, group_size: int,
+                   output_dtype: torch.dtype = torch.bfloat16) -> "WQLinear_GEMM":
+        """Quantise (asymmetric, per group) and pack a CUDA ``nn.Linear`` in one kernel.
+
+        Equal, word for word, to what the reference's quantizer does per layer
+        (awq/quantizer.py:150-170): ``pseudo_quantize`` of the weight
+        (utils/quantization.py:20-41), then ``from_linear`` on the fake-quantised
+        weight with the transposed scales and zero-points."""
+        if w_bits != 4:
+            raise ValueError("Only 4-bit quantization is supported")
+        w = linear_layer.weight.data
+        dev = _lib.require_cuda(w)
+        _lib.require_b200(dev)
+        wcode = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[w.dtype]
+        q = cls(w_bits, group_size, linear_layer.in_features, linear_layer.out_features, dev,
+                linear_layer.bias is not None, output_dtype)
+        if linear_layer.bias is not None:
+            q.bias = linear_layer.bias.clone().to(output_dtype)
+        w = _contig(w)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().nqb200_quantize_pack(w.data_ptr(), wcode, q.qweight.data_ptr(), q.qscales.data_ptr(),
+                                                        q.qzeros.data_ptr(), linear_layer.out_features,
+                                                        linear_layer.in_features, group_size,
+                                                        _lib.dtype_code(output_dtype), _lib.stream_ptr()))
+        return q
+
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """``[..., K] -> [..., N]``.  The reference switches kernels at 256 tokens

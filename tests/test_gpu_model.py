@@ -1,0 +1,72 @@
+"""The quantised Qwen3 model and the serving engine on a GPU (tiny random-init model)."""
+import pytest
+import torch
+
+import nanoquantization_b200 as nq
+from nanoquantization_b200.engine import LLMEngine
+from nanoquantization_b200.models import Qwen3QuantizedForCausalLM
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _tiny(dtype=torch.float16, seed=0):
+    torch.manual_seed(seed)
+    m = Qwen3QuantizedForCausalLM(2, 512, 256, 4, 2, 1024, 512, 4, 128, 64, False, 1e6, 1e-6, device=DEV, dtype=dtype)
+    g = torch.Generator(device=DEV); g.manual_seed(seed)
+    for mod in m.modules():
+        if isinstance(mod, nq.WQLinear_GEMM):
+            mod.qweight.copy_(torch.randint(-2 ** 31, 2 ** 31, mod.qweight.shape, generator=g, device=DEV, dtype=torch.int64).to(torch.int32))
+            mod.qzeros.copy_(torch.randint(-2 ** 31, 2 ** 31, mod.qzeros.shape, generator=g, device=DEV, dtype=torch.int64).to(torch.int32))
+            mod.qscales.copy_((torch.rand(mod.qscales.shape, generator=g, device=DEV) * 9e-3 + 1e-3).to(dtype))
+    return m
+
+
+def test_state_dict_keys_match_reference_names():
+    m = _tiny()
+    keys = set(m.state_dict().keys())
+    for k in ("model.embed_tokens.weight", "model.layers.0.self_attn.q_proj.qweight", "model.layers.0.self_attn.k_proj.qscales",
+              "model.layers.1.self_attn.o_proj.qzeros", "model.layers.0.self_attn.q_norm.weight",
+              "model.layers.0.mlp.gate_proj.qweight", "model.layers.1.mlp.down_proj.qscales",
+              "model.layers.0.input_layernorm.weight", "model.layers.1.post_attention_layernorm.weight",
+              "model.norm.weight", "lm_head.weight", "lm_head.bias"):
+        assert k in keys, k
+
+
+@torch.no_grad()
+def test_fused_projections_give_the_same_hidden_states():
+    m = _tiny()
+    x = torch.randint(0, 512, (2, 24), device=DEV)
+    pos = torch.arange(24, device=DEV).unsqueeze(0)
+    h0 = m(x, pos)
+    m.fuse_projections()
+    h1 = m(x, pos)
+    assert torch.isfinite(h0).all()
+    assert float((h0.float() - h1.float()).abs().max()) <= 2e-2 * float(h0.float().abs().max())
+
+
+@torch.no_grad()
+def test_engine_first_token_matches_full_forward_and_graphs_match_eager():
+    m = _tiny(seed=1)
+    m.fuse_projections()
+    prompts = [torch.randint(0, 512, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (5, 33, 17)]
+    # the reference-style path: full-sequence forward, arg-max of the last position
+    firsts = []
+    for p in prompts:
+        x = torch.tensor([p], device=DEV)
+        h = m(x, torch.arange(len(p), device=DEV).unsqueeze(0))
+        firsts.append(int(m.greedy_tokens(h[0, -1:])[0]))
+    eager = LLMEngine(m, num_blocks=32, block_size=16, use_cuda_graph=False).generate(prompts, 6)
+    graph = LLMEngine(m, num_blocks=32, block_size=16, use_cuda_graph=True).generate(prompts, 6)
+    assert [o[0] for o in eager] == firsts
+    assert eager == graph
+    assert all(len(o) == 6 for o in eager)
+
+
+def test_engine_continuous_batching_ragged_lengths():
+    m = _tiny(seed=2)
+    eng = LLMEngine(m, num_blocks=24, block_size=16, max_batch=3)
+    prompts = [[1 + i] * (4 + 3 * i) for i in range(5)]
+    outs = eng.generate(prompts, [2, 5, 3, 1, 4])
+    assert [len(o) for o in outs] == [2, 5, 3, 1, 4]
+    assert len(eng.blocks.free) == 24          # every block returned

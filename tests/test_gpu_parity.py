@@ -222,3 +222,23 @@ def test_gemm_linearity_property_full_size():
     assert torch.equal(y2[normal], (y1 * 2)[normal])
     assert float((y2.float() - 2 * y1.float()).abs().max()) <= 2.0 ** -23
     assert float(normal.float().mean()) > 0.99
+
+
+# ------------------------------------------------------- quantise + pack on the GPU
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float16, torch.float16), (torch.bfloat16, torch.bfloat16),
+                                           (torch.float32, torch.float16)])
+@pytest.mark.parametrize("K,N,g", [(1024, 2048, 32), (512, 136, 128), (256, 64, 64)])
+def test_quantize_pack_bit_exact_vs_reference_pipeline(wdtype, odtype, K, N, g):
+    # the reference's per-layer recipe on the CPU: pseudo_quantize, then from_linear on the
+    # fake-quantised weight with transposed scales / zero-points
+    w = torch.randn(N, K, generator=torch.Generator().manual_seed(K + N)).to(wdtype)
+    w[3, :g] = 0.25                                            # a constant group: range below the 1e-5 clamp
+    wq, s, z = O.pseudo_quantize(w.clone(), g, 4)
+    qw_ref, qs_ref, qz_ref = O.from_linear_ref(wq, s.t().contiguous(), z.t().contiguous(), g, odtype)
+    lin = torch.nn.Linear(K, N, bias=False, device=DEV, dtype=wdtype)
+    lin.weight.data.copy_(w)
+    m = nq.WQLinear_GEMM.from_float(lin, 4, g, odtype)
+    torch.cuda.synchronize()
+    assert np.array_equal(m.qzeros.cpu().numpy(), qz_ref.numpy())
+    assert np.array_equal(_bits(m.qscales), _bits(qs_ref))
+    assert np.array_equal(m.qweight.cpu().numpy(), qw_ref.numpy())
