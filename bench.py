@@ -284,6 +284,13 @@ def run_ours(args):
                           "kernel": lib.nqb200_gemm_kernel_name(M, n, k, GROUP, 0).decode()})
     clocks = sampler.stop() if rank == 0 else None
     barrier()
+    decode = None
+    if not args.no_decode:
+        for k in list(layers):
+            del layers[k]
+        torch.cuda.empty_cache()
+        decode = decode_bench(world, rank, dev, dtype)
+        barrier()
 
     if rank == 0:
         pk = peaks()
@@ -324,13 +331,86 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": len(points) * args.steps,
             "roofline": roof_prefill, "roofline_decode": roof_decode,
-            "clocks": clocks, "points": per_point,
+            "clocks": clocks, "points": per_point, "decode_qwen3_8b": decode,
         }
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(seconds_budget=20.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------
+# second half of the metric: Qwen3-8B-architecture AWQ decode tokens/s through the engine
+# --------------------------------------------------------------------------
+def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, steps=16):
+    """Random-init Qwen3-8B (w4 g128, tensor-parallel over `world` ranks), sequences with a
+    2048-token context in the paged KV cache, greedy decode steps replayed as a CUDA graph."""
+    import torch.distributed as dist
+    from nanoquantization_b200 import WQLinear_GEMM
+    from nanoquantization_b200.engine import LLMEngine, Sequence
+    from nanoquantization_b200.models import QWEN3_SHAPES, Qwen3QuantizedForCausalLM
+    shp = QWEN3_SHAPES["qwen3-8b"]
+    model = Qwen3QuantizedForCausalLM(shp["num_hidden_layers"], 151936, shp["hidden_size"], shp["total_num_heads"],
+                                      shp["total_num_kv_heads"], 8192, shp["intermediate_size"], 4, GROUP, 128, False, 1e6,
+                                      1e-6, tp_size=world, tp_rank=rank, device=dev, dtype=dtype)
+    n = 0
+    for mod in model.modules():
+        if isinstance(mod, WQLinear_GEMM):
+            fill_layer(mod, 5000 + n + 100 * rank, dev, dtype)
+            n += 1
+    torch.nn.init.normal_(model.model.embed_tokens.weight, std=0.02)
+    torch.nn.init.normal_(model.lm_head.weight, std=0.02)
+    model.fuse_projections()
+    block = 256
+    per_seq = -(-(context + steps + 8) // block)
+    eng = LLMEngine(model, num_blocks=max(batches) * per_seq + 4, block_size=block, max_batch=max(batches))
+    out = {"model": "qwen3-8b-arch w4 g128 random init", "tp": world, "context": context,
+           "attention": "flash_attn paged" if eng.paged_attention is not None else "sdpa over gathered pages", "points": []}
+    g = torch.Generator().manual_seed(1)
+    for B in batches:
+        seqs = []
+        for i in range(B):
+            s = Sequence(i, torch.randint(0, 151936, (context,), generator=g).tolist(), 10 ** 9)
+            assert eng.blocks.ensure(s, context + steps + 8)
+            s.output.append(1)
+            seqs.append(s)
+        for _ in range(3):
+            eng._decode(seqs)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            eng._decode(seqs)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        pt = {"batch": B, "ms_per_step": round(ms, 3), "tok_per_s": round(B / ms * 1e3, 1)}
+        if world > 1:  # share of the step spent in the 2 all-reduces per layer
+            buf = torch.zeros(B, shp["hidden_size"], dtype=dtype, device=dev)
+            gr = torch.cuda.CUDAGraph()
+            for _ in range(2 * shp["num_hidden_layers"]):
+                dist.all_reduce(buf)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(gr):
+                for _ in range(2 * shp["num_hidden_layers"]):
+                    dist.all_reduce(buf)
+            gr.replay(); torch.cuda.synchronize()
+            e0.record(); gr.replay(); e1.record(); torch.cuda.synchronize()
+            pt["allreduce_ms_per_step"] = round(e0.elapsed_time(e1), 3)
+            pt["allreduce_share"] = round(e0.elapsed_time(e1) / ms, 3)
+        out["points"].append(pt)
+        for s in seqs:
+            eng.blocks.release(s)
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
 
 
 # --------------------------------------------------------------------------
@@ -454,6 +534,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the Qwen3-8B decode tokens/s section")
     ap.add_argument("--point", default=None, help="M,K,N: run only this point (for profilers)")
     ap.add_argument("--reps", type=int, default=6)
     ap.add_argument("--no-graph", action="store_true", help="with --point: plain launches (what a profiler should see)")

@@ -106,6 +106,21 @@ int nqb200_gemm_decode_noalloc(const void* x, const void* qweight, const void* q
 int nqb200_quantize_pack(const void* weight, int weight_dtype, void* qweight, void* qscales, void* qzeros,
                          int64_t N, int64_t K, int64_t group_size, int scales_dtype, void* stream);
 
+/* Elementwise steps either side of the linears in a Qwen3 block, one launch each.
+ * nqb200_add_rmsnorm: h = x (+ residual); residual_out = h (may alias residual; may be NULL);
+ *   out = RMSNorm(h) * weight.  Replaces the residual adds models/qwen3_quantized.py:213-214 and
+ *   RMSNorm layers/norm.py:18-32.  x, residual, out: [T, H]; weight: [H].
+ * nqb200_qknorm_rope: in place on a fused [T, row_stride] buffer holding q heads, then k heads, then v:
+ *   per-head RMSNorm (models/qwen3_quantized.py:88) then rotary embedding (layers/rope.py:24-45) with the
+ *   fp32 table cos_sin [max_pos, head_dim] = cos | sin and int64 positions [T].  head_dim must be 128.
+ * nqb200_silu_mul: out[T, I] = silu(gate_up[:, :I]) * gate_up[:, I:] (models/qwen3_quantized.py:150). */
+int nqb200_add_rmsnorm(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
+                       int64_t T, int64_t H, float eps, int dtype, void* stream);
+int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                       const int64_t* positions, int64_t T, int64_t num_q_heads, int64_t num_kv_heads,
+                       int64_t head_dim, int64_t row_stride, float eps, int dtype, void* stream);
+int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_t I, int dtype, void* stream);
+
 /* Waits for `stream`, then returns the status the kernels recorded in this
  * workspace: NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a bounded device-side wait
  * (an mbarrier or a tile counter) gave up; the record is cleared.  The kernels

@@ -28,6 +28,9 @@ SIGNATURES = {
     "nqb200_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "nqb200_gemm_decode_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
     "nqb200_quantize_pack": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "nqb200_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _int, _vp]),
+    "nqb200_qknorm_rope": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _int, _vp]),
+    "nqb200_silu_mul": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "nqb200_workspace_status": (_int, [_vp, _sz, _vp]),
     "nqb200_gemm_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _i64, _int]),
 }

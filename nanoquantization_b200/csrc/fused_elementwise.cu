@@ -1,0 +1,147 @@
+// The elementwise steps either side of the linears in a Qwen3 block, one kernel
+// each instead of the 5-10 small launches PyTorch needs: residual add + RMSNorm,
+// per-head QK-norm + rotary embedding, SiLU(gate) * up.  At decode these launches
+// cost as much as the GEMVs.  Roundings follow the reference modules exactly
+// (nanoquantization/layers/norm.py:18-32, layers/rope.py:24-45,
+// models/qwen3_quantized.py:150,213-214): fp32 inside, one rounding to the
+// 16-bit type wherever the reference materialises a 16-bit tensor.
+#include "common.cuh"
+
+namespace nqb200 {
+
+template <bool BF16> __device__ __forceinline__ float rnd16(float v) { return raw16_to_float<BF16>(float_to_raw16<BF16>(v)); }
+
+// One CTA per token.  h = x (+ residual), rounded; residual_out = h; out = (round16(h * rsqrt(mean(h^2)+eps))) * w.
+template <bool BF16>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* residual,
+                                                          const uint16_t* __restrict__ weight, uint16_t* __restrict__ out,
+                                                          uint16_t* residual_out, int H, float eps) {
+  extern __shared__ float hbuf[];  // H floats
+  __shared__ float red[8];
+  const size_t row = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float h = raw16_to_float<BF16>(x[row + i]);
+    if (residual) h = rnd16<BF16>(h + raw16_to_float<BF16>(residual[row + i]));
+    if (residual_out) residual_out[row + i] = float_to_raw16<BF16>(h);
+    hbuf[i] = h;
+    ss += h * h;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += red[w];
+  const float inv = rsqrtf(tot / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[row + i] = float_to_raw16<BF16>(rnd16<BF16>(hbuf[i] * inv) * raw16_to_float<BF16>(weight[i]));
+}
+
+// One warp per (token, head) of q and k inside a fused [T, (Hq + 2*Hkv) * D] buffer, D = 128, in place:
+// RMSNorm over the head (weight qw / kw), then the half-split rotation with the fp32 cos|sin table row
+// of the token's position.  v is untouched.
+template <bool BF16>
+__global__ void __launch_bounds__(256) qknorm_rope_kernel(uint16_t* __restrict__ qkv, const uint16_t* __restrict__ qw,
+                                                          const uint16_t* __restrict__ kw, const float* __restrict__ cos_sin,
+                                                          const int64_t* __restrict__ positions, int T, int Hq, int Hkv,
+                                                          int row_stride, float eps) {
+  constexpr int D = 128;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = Hq + Hkv;
+  if (gw >= T * heads) return;
+  const int t = gw / heads, hd = gw % heads;
+  uint16_t* p = qkv + (size_t)t * row_stride + (size_t)hd * D;  // q heads first, then k heads
+  const uint16_t* w = hd < Hq ? qw : kw;
+  // lane owns elements lane, lane+32, lane+64, lane+96: (lane, lane+64) and (lane+32, lane+96) are rotation pairs
+  float v[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = raw16_to_float<BF16>(p[lane + 32 * j]); ss += v[j] * v[j]; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    v[j] = rnd16<BF16>(rnd16<BF16>(v[j] * inv) * raw16_to_float<BF16>(w[lane + 32 * j]));
+  const float* cs = cos_sin + (size_t)positions[t] * D;  // [cos(64) | sin(64)]
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = lane + 32 * j;
+    const float c = cs[i], s = cs[64 + i];
+    const float a = v[j], b = v[j + 2];
+    p[i] = float_to_raw16<BF16>(a * c - b * s);
+    p[i + 64] = float_to_raw16<BF16>(a * s + b * c);
+  }
+}
+
+// out[t, i] = round16(silu(gate)) * up, gate = gate_up[t, i], up = gate_up[t, I + i]
+template <bool BF16>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out,
+                                                       int64_t T, int I) {
+  const int64_t total = T * (int64_t)I;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = raw16_to_float<BF16>(gate_up[t * 2 * I + i]);
+    const float u = raw16_to_float<BF16>(gate_up[t * 2 * I + I + i]);
+    const float s = rnd16<BF16>(g / (1.f + expf(-g)));
+    out[idx] = float_to_raw16<BF16>(s * u);
+  }
+}
+
+}  // namespace nqb200
+
+using namespace nqb200;
+
+extern "C" int nqb200_add_rmsnorm(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
+                                  int64_t T, int64_t H, float eps, int dtype, void* stream) {
+  if (T < 0 || H <= 0 || H > 65536) return NQB200_ERR_BAD_SHAPE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  if (T == 0) return NQB200_OK;
+  if (!x || !weight || !out) return NQB200_ERR_NULL_POINTER;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (dtype == NQB200_BF16)
+    add_rmsnorm_kernel<true><<<(unsigned)T, 256, smem, st>>>((const uint16_t*)x, (const uint16_t*)residual, (const uint16_t*)weight,
+                                                             (uint16_t*)out, (uint16_t*)residual_out, (int)H, eps);
+  else
+    add_rmsnorm_kernel<false><<<(unsigned)T, 256, smem, st>>>((const uint16_t*)x, (const uint16_t*)residual, (const uint16_t*)weight,
+                                                              (uint16_t*)out, (uint16_t*)residual_out, (int)H, eps);
+  return check_launch();
+}
+
+extern "C" int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                                  const int64_t* positions, int64_t T, int64_t num_q_heads, int64_t num_kv_heads,
+                                  int64_t head_dim, int64_t row_stride, float eps, int dtype, void* stream) {
+  if (T < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim != 128) return NQB200_ERR_BAD_SHAPE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  if (T == 0) return NQB200_OK;
+  if (!qkv || !q_weight || !k_weight || !cos_sin || !positions) return NQB200_ERR_NULL_POINTER;
+  const int64_t warps = T * (num_q_heads + num_kv_heads);
+  const unsigned blocks = (unsigned)((warps + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NQB200_BF16)
+    qknorm_rope_kernel<true><<<blocks, 256, 0, st>>>((uint16_t*)qkv, (const uint16_t*)q_weight, (const uint16_t*)k_weight, cos_sin,
+                                                     positions, (int)T, (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps);
+  else
+    qknorm_rope_kernel<false><<<blocks, 256, 0, st>>>((uint16_t*)qkv, (const uint16_t*)q_weight, (const uint16_t*)k_weight, cos_sin,
+                                                      positions, (int)T, (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps);
+  return check_launch();
+}
+
+extern "C" int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_t I, int dtype, void* stream) {
+  if (T < 0 || I <= 0 || I > INT32_MAX) return NQB200_ERR_BAD_SHAPE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  if (T == 0) return NQB200_OK;
+  if (!gate_up || !out) return NQB200_ERR_NULL_POINTER;
+  const int64_t total = T * I;
+  const int64_t want = (total + 255) / 256;
+  const unsigned blocks = (unsigned)(want < (int64_t)kNumSMs * 16 ? want : (int64_t)kNumSMs * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == NQB200_BF16) silu_mul_kernel<true><<<blocks, 256, 0, st>>>((const uint16_t*)gate_up, (uint16_t*)out, T, (int)I);
+  else silu_mul_kernel<false><<<blocks, 256, 0, st>>>((const uint16_t*)gate_up, (uint16_t*)out, T, (int)I);
+  return check_launch();
+}

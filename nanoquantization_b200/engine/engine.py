@@ -150,10 +150,25 @@ class LLMEngine:
         self.blocks = BlockManager(num_blocks, block_size)
         self.scheduler = Scheduler(self.blocks, max_batch, max_prefill_tokens)
         self.use_cuda_graph = use_cuda_graph
+        self.paged_attention = self._probe_flash_attn() if block_size % 256 == 0 else None
         self._graphs: dict[tuple[int, int], tuple] = {}
         self._next_id = 0
 
     # ------------------------------------------------------------------ attention
+    def _probe_flash_attn(self):
+        """flash_attn's paged decode kernel if this build of it runs on this GPU, else None (the
+        fallback gathers the pages and calls scaled_dot_product_attention)."""
+        try:
+            from flash_attn import flash_attn_with_kvcache
+            q = torch.zeros(1, 1, self.q_heads, self.head_dim, dtype=self.dtype, device=self.device)
+            bt = torch.zeros(1, 1, dtype=torch.int32, device=self.device)
+            ln = torch.ones(1, dtype=torch.int32, device=self.device)
+            flash_attn_with_kvcache(q, self.cache.k[0], self.cache.v[0], cache_seqlens=ln, block_table=bt, causal=True)
+            torch.cuda.synchronize()
+            return flash_attn_with_kvcache
+        except Exception:  # not built for this architecture, or not importable
+            return None
+
     def _prefill_attend(self, layer: int, slots: torch.Tensor, lens: list[int]) -> Callable:
         def attend(q, k, v):
             self.cache.write(layer, slots, k, v)
@@ -167,10 +182,13 @@ class LLMEngine:
         return attend
 
     def _decode_attend(self, layer: int, slots: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor,
-                       max_blocks: int) -> Callable:
+                       max_blocks: int, ctx_i32=None, bt_i32=None) -> Callable:
         def attend(q, k, v):
             self.cache.write(layer, slots, k, v)
             B = q.shape[0]
+            if self.paged_attention is not None:
+                return self.paged_attention(q.unsqueeze(1), self.cache.k[layer], self.cache.v[layer],
+                                            cache_seqlens=ctx_i32, block_table=bt_i32, causal=True).squeeze(1)
             kk = self.cache.k[layer][block_tables[:, :max_blocks]].reshape(B, -1, self.kv_heads, self.head_dim)
             vv = self.cache.v[layer][block_tables[:, :max_blocks]].reshape(B, -1, self.kv_heads, self.head_dim)
             S = kk.shape[1]
@@ -212,7 +230,11 @@ class LLMEngine:
         return toks, pos, slots, bt, ctx
 
     def _decode_forward(self, toks, pos, slots, bt, ctx, max_blocks):
-        h = self.model.model.forward_tokens(toks, pos, lambda i: self._decode_attend(i, slots, bt, ctx, max_blocks))
+        ctx_i32, bt_i32 = None, None
+        if self.paged_attention is not None:  # once per step, not once per layer
+            ctx_i32, bt_i32 = ctx.to(torch.int32), bt[:, :max_blocks].to(torch.int32).contiguous()
+        h = self.model.model.forward_tokens(
+            toks, pos, lambda i: self._decode_attend(i, slots, bt, ctx, max_blocks, ctx_i32, bt_i32))
         return self.model.greedy_tokens(h)
 
     @torch.no_grad()

@@ -26,6 +26,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..layers import fused
 from ..layers.gemm import WQLinear_GEMM
 
 
@@ -146,14 +147,25 @@ class Qwen3QuantizedAttention(nn.Module):
         return _all_reduce(self.o_proj(o), self.tp_size, self.tp_group)
 
     def forward_tokens(self, x: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
-        """``x`` is ``[T, hidden]``; ``attend(q, k, v)`` stores k, v in its cache and returns ``[T, Hq, D]``."""
+        """``x`` is ``[T, hidden]``; ``attend(q, k, v)`` stores k, v in its cache and returns ``[T, Hq, D]``.
+        One launch for q/k/v (when fused), one for QK-norm + rotary embedding."""
         T = x.shape[0]
-        q, k, v = self._qkv(x)
-        q = self.q_norm(q.view(T, self.num_heads, self.head_dim))
-        k = self.k_norm(k.view(T, self.num_kv_heads, self.head_dim))
-        v = v.view(T, self.num_kv_heads, self.head_dim)
-        q, k = self.rope(q, k, positions)
-        o = attend(q, k, v).reshape(T, self.num_heads * self.head_dim)
+        nq, nk = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        if self.qkv_proj is not None:
+            qkv = self.qkv_proj(x)
+        else:
+            qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], dim=-1)
+        if self.head_dim == 128:
+            fused.qknorm_rope_(qkv, self.q_norm.weight, self.k_norm.weight, self.rope.cos_sin_cache, positions,
+                               self.num_heads, self.num_kv_heads, self.head_dim, self.q_norm.eps)
+            q = qkv[:, :nq].view(T, self.num_heads, self.head_dim)
+            k = qkv[:, nq:nq + nk].view(T, self.num_kv_heads, self.head_dim)
+        else:
+            q = self.q_norm(qkv[:, :nq].reshape(T, self.num_heads, self.head_dim))
+            k = self.k_norm(qkv[:, nq:nq + nk].reshape(T, self.num_kv_heads, self.head_dim))
+            q, k = self.rope(q, k, positions)
+        v = qkv[:, nq + nk:].view(T, self.num_kv_heads, self.head_dim)
+        o = attend(q, k, v).reshape(T, nq)
         return _all_reduce(self.o_proj(o), self.tp_size, self.tp_group)
 
 
@@ -187,6 +199,11 @@ class Qwen3QuantizedMLP(nn.Module):
             y1, y2 = self.gate_proj(x), self.up_proj(x)
         return _all_reduce(self.down_proj(F.silu(y1) * y2), self.tp_size, self.tp_group)
 
+    def forward_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        if self.gate_up_proj is None:
+            return self.forward(x)
+        return _all_reduce(self.down_proj(fused.silu_mul(self.gate_up_proj(x))), self.tp_size, self.tp_group)
+
 
 class Qwen3QuantizedBlock(nn.Module):
     def __init__(self, hidden_size, total_num_heads, total_num_kv_heads, max_position_embeddings, intermediate_size,
@@ -202,9 +219,12 @@ class Qwen3QuantizedBlock(nn.Module):
         x = x + self.self_attn(self.input_layernorm(x), position_ids)
         return x + self.mlp(self.post_attention_layernorm(x))
 
-    def forward_tokens(self, x, positions, attend):
-        x = x + self.self_attn.forward_tokens(self.input_layernorm(x), positions, attend)
-        return x + self.mlp(self.post_attention_layernorm(x))
+    def forward_tokens(self, x, residual, positions, attend):
+        """``x`` is the previous sub-layer's output still to be added to the residual stream."""
+        h, residual = fused.add_rmsnorm(x, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+        a = self.self_attn.forward_tokens(h, positions, attend)
+        h, residual = fused.add_rmsnorm(a, residual, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps)
+        return self.mlp.forward_tokens(h), residual
 
 
 class Qwen3QuantizedModel(nn.Module):
@@ -227,10 +247,10 @@ class Qwen3QuantizedModel(nn.Module):
         return self.norm(x)
 
     def forward_tokens(self, token_ids, positions, attend_for_layer: Callable[[int], Callable]):
-        x = self.embed_tokens(token_ids)
+        x, residual = self.embed_tokens(token_ids), None
         for i, layer in enumerate(self.layers):
-            x = layer.forward_tokens(x, positions, attend_for_layer(i))
-        return self.norm(x)
+            x, residual = layer.forward_tokens(x, residual, positions, attend_for_layer(i))
+        return fused.add_rmsnorm(x, residual, self.norm.weight, self.norm.eps)[0]
 
 
 class Qwen3QuantizedForCausalLM(nn.Module):

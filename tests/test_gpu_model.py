@@ -70,3 +70,44 @@ def test_engine_continuous_batching_ragged_lengths():
     outs = eng.generate(prompts, [2, 5, 3, 1, 4])
     assert [len(o) for o in outs] == [2, 5, 3, 1, 4]
     assert len(eng.blocks.free) == 24          # every block returned
+
+
+# ------------------------------------------------------------ fused elementwise kernels
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@torch.no_grad()
+def test_fused_kernels_match_reference_modules(dtype):
+    from nanoquantization_b200.layers import fused
+    from nanoquantization_b200.models import RMSNorm, RotaryCache
+    g = torch.Generator(device=DEV).manual_seed(3)
+    T, H, Hq, Hkv, D, I = 7, 1024, 4, 2, 128, 768
+    ulp = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
+
+    def close(a, b):
+        return float((a.float() - b.float()).abs().max()) <= 2 * ulp * max(1.0, float(b.float().abs().max()))
+
+    x = torch.randn(T, H, generator=g, device=DEV).to(dtype)
+    r = torch.randn(T, H, generator=g, device=DEV).to(dtype)
+    norm = RMSNorm(H, 1e-6).to(DEV)
+    norm.weight.data = (torch.rand(H, generator=g, device=DEV) + 0.5).to(dtype)
+    out, res = fused.add_rmsnorm(x, r.clone(), norm.weight, 1e-6)
+    assert torch.equal(res, x + r) and close(out, norm(x + r))
+    out0, res0 = fused.add_rmsnorm(x, None, norm.weight, 1e-6)
+    assert res0 is x and close(out0, norm(x))
+
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g, device=DEV).to(dtype)
+    qn, kn = RMSNorm(D, 1e-6).to(DEV), RMSNorm(D, 1e-6).to(DEV)
+    qn.weight.data = (torch.rand(D, generator=g, device=DEV) + 0.5).to(dtype)
+    kn.weight.data = (torch.rand(D, generator=g, device=DEV) + 0.5).to(dtype)
+    rope = RotaryCache(D, 4096, 1e6).to(DEV)
+    pos = torch.tensor([0, 1, 5, 100, 1000, 4095, 17], device=DEV)
+    q_ref = qn(qkv[:, :Hq * D].reshape(T, Hq, D))
+    k_ref = kn(qkv[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D))
+    q_ref, k_ref = rope(q_ref, k_ref, pos)
+    v_ref = qkv[:, (Hq + Hkv) * D:].clone()
+    fused.qknorm_rope_(qkv, qn.weight, kn.weight, rope.cos_sin_cache, pos, Hq, Hkv, D, 1e-6)
+    assert close(qkv[:, :Hq * D].reshape(T, Hq, D), q_ref)
+    assert close(qkv[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D), k_ref)
+    assert torch.equal(qkv[:, (Hq + Hkv) * D:], v_ref)
+
+    gu = torch.randn(T, 2 * I, generator=g, device=DEV).to(dtype)
+    assert close(fused.silu_mul(gu), torch.nn.functional.silu(gu[:, :I]) * gu[:, I:])
