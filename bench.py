@@ -335,9 +335,15 @@ def run_ours(args):
         }
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(seconds_budget=20.0)
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a communicator whose all-reduces were captured in
+        # CUDA graphs has been seen to block for ever at exit.  Every rank has finished its work here.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # --------------------------------------------------------------------------
@@ -489,7 +495,7 @@ def run_reference(args):
             "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0, "wall_s": round(time.perf_counter() - t0, 1)}
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 def run_point(args):
@@ -524,8 +530,27 @@ def run_point(args):
     torch.cuda.synchronize()
     _lib.check_workspaces()
     us = e0.elapsed_time(e1) * 1e3 / args.reps
-    print(json.dumps({"point": [M, K, N], "reps": args.reps, "us_per_call_incl_launch": round(us, 2),
+    emit(json.dumps({"point": [M, K, N], "reps": args.reps, "us_per_call_incl_launch": round(us, 2),
                       "kernel": _lib.load().nqb200_gemm_kernel_name(M, N, K, GROUP, 0).decode()}))
+
+
+_REAL_STDOUT = None
+
+
+def protect_stdout():
+    """Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line
+    there.  Everything written to fd 1 from here on goes to stderr; emit() writes to the real stdout."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(text: str) -> None:
+    if _REAL_STDOUT is None:
+        print(text, flush=True)
+    else:
+        os.write(_REAL_STDOUT, (text + "\n").encode())
 
 
 def main():
@@ -540,6 +565,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="with --point: plain launches (what a profiler should see)")
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     args = ap.parse_args()
+    protect_stdout()
     if args.point:
         run_point(args)
     elif args.impl == "reference":
