@@ -374,7 +374,14 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
     out = {"model": "qwen3-8b-arch w4 g128 random init", "tp": world, "context": context,
            "attention": "flash_attn paged" if eng.paged_attention is not None else "sdpa over gathered pages", "points": []}
     g = torch.Generator().manual_seed(1)
-    for B in batches:
+    comm = None
+    if world > 1:
+        from nanoquantization_b200.layers.peer_comm import PeerAllReduce
+        comm = PeerAllReduce(slot_bytes=1 << 20, num_slots=8)   # 72 all-reduces per step: a multiple of the slot count
+    variants = [("nccl", None)] + ([("peer", comm)] if comm is not None else [])
+    for (ar_name, ar_comm), B in [(v, b) for v in variants for b in batches]:
+        model.attach_peer_comm(ar_comm)
+        eng._graphs.clear()
         seqs = []
         for i in range(B):
             s = Sequence(i, torch.randint(0, 151936, (context,), generator=g).tolist(), 10 ** 9)
@@ -398,7 +405,9 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         pt = {"batch": B, "ms_per_step": round(ms, 3), "tok_per_s": round(B / ms * 1e3, 1)}
-        if world > 1:  # share of the step spent in the 2 all-reduces per layer
+        if world > 1:
+            pt["allreduce"] = ar_name
+        if world > 1 and ar_name == "nccl":  # share of the step spent in the 2 all-reduces per layer
             buf = torch.zeros(B, shp["hidden_size"], dtype=dtype, device=dev)
             gr = torch.cuda.CUDAGraph()
             for _ in range(2 * shp["num_hidden_layers"]):
@@ -414,6 +423,8 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
         out["points"].append(pt)
         for s in seqs:
             eng.blocks.release(s)
+    if comm is not None:
+        out["peer_allreduce_status"] = comm.status()
     del eng, model
     torch.cuda.empty_cache()
     return out

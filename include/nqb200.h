@@ -121,6 +121,27 @@ int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, co
                        int64_t head_dim, int64_t row_stride, float eps, int dtype, void* stream);
 int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_t I, int dtype, void* stream);
 
+/* One-shot all-reduce (sum) over NVLink peer memory for the small [M, N] partial results of a
+ * row-parallel linear.  No counterpart in the reference (it has no distributed code).
+ * Set-up, once: every rank calls nqb200_comm_alloc (a cudaMalloc'd, zeroed buffer: a header of
+ * nqb200_comm_data_offset() bytes, then `data_bytes` of slots), exports it with nqb200_comm_export
+ * (a 64-byte CUDA IPC handle), exchanges handles with its peers by any host channel, and maps each
+ * peer's buffer with nqb200_comm_import.  Per call: every rank's GEMM writes its partial result at
+ * `slot_offset` inside its own data region, then every rank calls nqb200_peer_allreduce with the
+ * same arguments (peer_buffers[r] = rank r's buffer as mapped here; peer_buffers[rank] = its own).
+ * The kernel waits (at most about a second; then the first int of the rank's buffer holds
+ * NQB200_ERR_WAIT_TIMEOUT) until all ranks have arrived, then adds the slots in rank order and an
+ * optional bias and writes `out` in local memory.  Use slots round-robin: a slot may be rewritten
+ * once two later calls have been issued.  M * N must be a multiple of 8. */
+int nqb200_comm_alloc(void** ptr, size_t data_bytes);
+int nqb200_comm_free(void* ptr);
+int nqb200_comm_export(void* ptr, void* handle64);
+int nqb200_comm_import(const void* handle64, void** ptr);
+int nqb200_comm_unimport(void* ptr);
+size_t nqb200_comm_data_offset(void);
+int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int world, size_t slot_offset, void* out,
+                          const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype, void* stream);
+
 /* Waits for `stream`, then returns the status the kernels recorded in this
  * workspace: NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a bounded device-side wait
  * (an mbarrier or a tile counter) gave up; the record is cleared.  The kernels

@@ -31,6 +31,13 @@ SIGNATURES = {
     "nqb200_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _int, _vp]),
     "nqb200_qknorm_rope": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _int, _vp]),
     "nqb200_silu_mul": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
+    "nqb200_comm_alloc": (_int, [ctypes.POINTER(_vp), _sz]),
+    "nqb200_comm_free": (_int, [_vp]),
+    "nqb200_comm_export": (_int, [_vp, _vp]),
+    "nqb200_comm_import": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "nqb200_comm_unimport": (_int, [_vp]),
+    "nqb200_comm_data_offset": (_sz, []),
+    "nqb200_peer_allreduce": (_int, [ctypes.POINTER(_vp), _int, _int, _sz, _vp, _vp, _int, _i64, _i64, _int, _vp]),
     "nqb200_workspace_status": (_int, [_vp, _sz, _vp]),
     "nqb200_gemm_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _i64, _int]),
 }

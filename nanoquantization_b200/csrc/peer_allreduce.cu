@@ -1,0 +1,155 @@
+// One-shot all-reduce over NVLink peer memory for the small messages of
+// tensor-parallel decode (the [tokens, hidden] partial sums after a row-parallel
+// linear: 8 KB to 512 KB).  NCCL's per-call latency is most of its cost at these
+// sizes; here every rank's row-parallel GEMM writes its partial result straight
+// into a slot of a buffer that all peers have mapped, and one kernel per rank
+//   1. tells every peer "my slot holds call number e" and waits until every peer
+//      has said the same (flags in peer memory, one set per CTA),
+//   2. reads the same slot of every peer with plain loads and adds them in rank
+//      order (so all ranks get identical bits), writing the sum to local memory.
+// Slots are used round-robin, so a slot is rewritten only several calls later,
+// by which time every peer has passed the barrier of a later call and therefore
+// finished reading it; no closing barrier is needed.  The call number lives in
+// device memory and is advanced by the kernel itself, so the kernel can be
+// replayed from a CUDA graph.
+//
+// Waits are bounded (about one second): on expiry the kernel records
+// NQB200_ERR_WAIT_TIMEOUT in the rank's status word and returns without hanging.
+// Only plain peer loads and stores are used: no multimem, no TMA.
+#include "common.cuh"
+#include "tma_utils.cuh"
+
+namespace nqb200 {
+
+constexpr int kMaxRanks = 8;
+constexpr int kArBlocks = 32;            // CTAs per call; each has its own flag set
+constexpr int kArThreads = 256;
+// layout of a rank's comm buffer: [status 256 B][epochs kArBlocks x u32, padded to 256 B]
+//                                  [flags kArBlocks x kMaxRanks x u32][data slots]
+constexpr size_t kArOffEpoch = 256, kArOffFlags = 512, kArOffData = 4096;
+
+struct ArParams {
+  uint8_t* peers[kMaxRanks];   // every rank's comm buffer as mapped into this process (peers[rank] is our own)
+  int rank, world;
+  size_t slot_off;             // byte offset of the slot inside the data region
+  void* out;
+  const void* bias;            // optional, added once after the sum
+  int bias_dtype;
+  int64_t n;                   // elements (multiple of 8)
+  int N;                       // row length, for the bias
+};
+
+__device__ __forceinline__ void st_flag(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_flag(const uint32_t* p) {
+  uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ uint4 ld_peer(const uint4* p) {
+  uint4 v; asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const ArParams p) {
+  uint8_t* mine = p.peers[p.rank];
+  uint32_t* my_epoch = reinterpret_cast<uint32_t*>(mine + kArOffEpoch) + blockIdx.x;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) { s_epoch = *my_epoch + 1; *my_epoch = s_epoch; s_ok = 1; }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  if (threadIdx.x < p.world) {
+    // announce: flag [block][my rank] in peer threadIdx.x's buffer
+    uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peers[threadIdx.x] + kArOffFlags) + blockIdx.x * kMaxRanks + p.rank;
+    st_flag(theirs, e);
+    // wait for peer threadIdx.x's announcement in our buffer
+    const uint32_t* ours = reinterpret_cast<const uint32_t*>(mine + kArOffFlags) + blockIdx.x * kMaxRanks + threadIdx.x;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t it = 0;
+    // flags only grow; a peer that is already one call ahead shows e + 1
+    while ((int32_t)(ld_flag(ours) - e) < 0) {
+      if ((++it & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) {
+        atomicExch(reinterpret_cast<int*>(mine), NQB200_ERR_WAIT_TIMEOUT);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int64_t nvec = p.n >> 3;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int r = 0; r < p.world; ++r) {
+      const uint4 v = ld_peer(reinterpret_cast<const uint4*>(p.peers[r] + kArOffData + p.slot_off) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += raw16_to_float<BF16>((uint16_t)(w[j] & 0xFFFF));
+        acc[2 * j + 1] += raw16_to_float<BF16>((uint16_t)(w[j] >> 16));
+      }
+    }
+    if (p.bias) {
+      const int n0 = (int)((i * 8) % p.N);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += bias_to_float(p.bias, p.bias_dtype, n0 + j);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = (uint32_t)float_to_raw16<BF16>(acc[2 * j]) | ((uint32_t)float_to_raw16<BF16>(acc[2 * j + 1]) << 16);
+    reinterpret_cast<uint4*>(p.out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace nqb200
+
+using namespace nqb200;
+
+// ---- set-up helpers (these, and only these, allocate: a communication buffer is created once) ----
+extern "C" int nqb200_comm_alloc(void** ptr, size_t data_bytes) {
+  if (!ptr) return NQB200_ERR_NULL_POINTER;
+  const size_t total = kArOffData + data_bytes;
+  if (cudaMalloc(ptr, total) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  if (cudaMemset(*ptr, 0, total) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  return NQB200_OK;
+}
+extern "C" int nqb200_comm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? NQB200_OK : NQB200_ERR_LAUNCH; }
+extern "C" int nqb200_comm_export(void* ptr, void* handle64) {
+  if (!ptr || !handle64) return NQB200_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  memcpy(handle64, &h, sizeof(h));
+  return NQB200_OK;
+}
+extern "C" int nqb200_comm_import(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) return NQB200_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  return NQB200_OK;
+}
+extern "C" int nqb200_comm_unimport(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? NQB200_OK : NQB200_ERR_LAUNCH; }
+extern "C" size_t nqb200_comm_data_offset(void) { return kArOffData; }
+
+extern "C" int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int world, size_t slot_offset, void* out,
+                                     const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return NQB200_ERR_BAD_SHAPE;
+  if (M < 0 || N <= 0 || (M * N) % 8 != 0 || slot_offset % 16 != 0) return NQB200_ERR_BAD_SHAPE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  if (M == 0) return NQB200_OK;
+  if (!peer_buffers || !out) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(out)) return NQB200_ERR_MISALIGNED;
+  ArParams p;
+  for (int r = 0; r < kMaxRanks; ++r) p.peers[r] = r < world ? (uint8_t*)peer_buffers[r] : nullptr;
+  for (int r = 0; r < world; ++r) if (!p.peers[r]) return NQB200_ERR_NULL_POINTER;
+  p.rank = rank; p.world = world; p.slot_off = slot_offset; p.out = out; p.bias = bias; p.bias_dtype = bias_dtype;
+  p.n = M * N; p.N = (int)N;
+  cudaStream_t st = (cudaStream_t)stream;
+  // always the same number of CTAs: each CTA has its own flags and call counter
+  if (dtype == NQB200_BF16) peer_allreduce_kernel<true><<<kArBlocks, kArThreads, 0, st>>>(p);
+  else peer_allreduce_kernel<false><<<kArBlocks, kArThreads, 0, st>>>(p);
+  return check_launch();
+}

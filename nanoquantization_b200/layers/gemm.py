@@ -82,8 +82,9 @@ _ws_bytes_cache: dict[tuple, int] = {}
 
 
 def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros: torch.Tensor,
-           bias: torch.Tensor | None) -> torch.Tensor:
-    """One fused call: out = x @ ((q - z) * s) (+ bias), any M."""
+           bias: torch.Tensor | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One fused call: out = x @ ((q - z) * s) (+ bias), any M.  ``out`` may name a preallocated
+    contiguous ``[M, N]`` tensor of the output dtype (e.g. a slot of a peer-mapped buffer)."""
     M, K = x.shape
     N = qweight.shape[1] * 8
     group_size = K // qscales.shape[0]
@@ -98,7 +99,10 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
     if bias is not None:
         bias = _contig(bias)
         bias_ptr, bias_code = bias.data_ptr(), _lib.dtype_code(bias.dtype)
-    out = torch.empty(M, N, dtype=dtype, device=dev)
+    if out is None:
+        out = torch.empty(M, N, dtype=dtype, device=dev)
+    else:
+        assert out.shape == (M, N) and out.dtype == dtype and out.is_contiguous()
     if M == 0:
         return out
     lib = _lib.load()
@@ -264,13 +268,13 @@ class WQLinear_GEMM(nn.Module):
         return q
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """``[..., K] -> [..., N]``.  The reference switches kernels at 256 tokens
         (gemm.py:558-564); here one library call picks the kernel by M, and the
         bias add (gemm.py:565-566) is fused into it."""
         out_shape = x.shape[:-1] + (self.out_features,)
         x = x.reshape(-1, x.shape[-1])
-        out = _w4a16(x, self.qweight, self.qscales, self.qzeros, self.bias)
+        out = _w4a16(x, self.qweight, self.qscales, self.qzeros, self.bias, out)
         return out.reshape(out_shape)
 
     def extra_repr(self) -> str:

@@ -1,0 +1,99 @@
+"""One-shot all-reduce over NVLink peer memory for tensor-parallel decode.
+
+``PeerAllReduce`` owns a cudaMalloc'd buffer per rank that every peer maps through CUDA IPC.  A
+row-parallel linear writes its partial ``[M, N]`` result straight into a slot of that buffer
+(``WQLinear_GEMM.forward(x, out=slot)``) and ``reduce`` launches one kernel per rank that waits
+for all ranks, adds the peers' slots in rank order and writes the sum to an ordinary tensor.
+Messages larger than a slot go through NCCL.  The reference has no counterpart.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+
+
+class _DevicePtr:
+    """Lets torch wrap a raw device pointer (``__cuda_array_interface__``) without copying."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerAllReduce:
+    def __init__(self, group=None, slot_bytes: int = 1 << 20, num_slots: int = 8):
+        assert num_slots >= 3
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.slot_bytes, self.num_slots, self._next = slot_bytes, num_slots, 0
+        lib = _lib.load()
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        own = ctypes.c_void_p()
+        _lib.check(lib.nqb200_comm_alloc(ctypes.byref(own), slot_bytes * num_slots))
+        self._own = own.value
+        handle = ctypes.create_string_buffer(64)
+        _lib.check(lib.nqb200_comm_export(self._own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._ptrs = (ctypes.c_void_p * self.world)()
+        self._imported = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self._ptrs[r] = self._own
+            else:
+                p = ctypes.c_void_p()
+                _lib.check(lib.nqb200_comm_import(ctypes.create_string_buffer(h, 64), ctypes.byref(p)))
+                self._ptrs[r] = p.value
+                self._imported.append(p.value)
+        self._data_off = lib.nqb200_comm_data_offset()
+        self._bytes = torch.as_tensor(_DevicePtr(self._own + self._data_off, slot_bytes * num_slots), device=self.device)
+        dist.barrier(group=group)
+
+    def fits(self, M: int, N: int) -> bool:
+        return M * N * 2 <= self.slot_bytes and (M * N) % 8 == 0
+
+    def next_slot(self, M: int, N: int, dtype: torch.dtype) -> tuple[torch.Tensor, int]:
+        """A ``[M, N]`` view of the next slot of this rank's buffer and its byte offset."""
+        off = self._next * self.slot_bytes
+        self._next = (self._next + 1) % self.num_slots
+        return self._bytes[off:off + M * N * 2].view(dtype).view(M, N), off
+
+    def reduce(self, slot_offset: int, M: int, N: int, dtype: torch.dtype, bias: torch.Tensor | None = None) -> torch.Tensor:
+        out = torch.empty(M, N, dtype=dtype, device=self.device)
+        _lib.check(_lib.load().nqb200_peer_allreduce(
+            self._ptrs, self.rank, self.world, slot_offset, out.data_ptr(),
+            bias.data_ptr() if bias is not None else None, _lib.dtype_code(bias.dtype) if bias is not None else 0,
+            M, N, _lib.dtype_code(dtype), _lib.stream_ptr()))
+        return out
+
+    def linear_all_reduce(self, linear, x: torch.Tensor) -> torch.Tensor:
+        """``all_reduce(linear(x))`` with the partial result written straight into peer-visible memory."""
+        M, N = x.shape[0], linear.out_features
+        if self.world == 1:
+            return linear(x)
+        if not self.fits(M, N):
+            y = linear(x)
+            dist.all_reduce(y, group=self.group)
+            return y
+        slot, off = self.next_slot(M, N, linear.qscales.dtype)
+        linear(x, out=slot)
+        return self.reduce(off, M, N, linear.qscales.dtype)
+
+    def status(self) -> int:
+        """0, or the code a bounded wait recorded when it gave up (synchronises)."""
+        torch.cuda.synchronize()
+        word = torch.as_tensor(_DevicePtr(self._own, 4), device=self.device).view(torch.int32)
+        return int(word.item())
+
+    def close(self) -> None:
+        lib = _lib.load()
+        torch.cuda.synchronize()
+        for p in self._imported:
+            lib.nqb200_comm_unimport(p)
+        self._imported = []
+        if self._own:
+            lib.nqb200_comm_free(self._own)
+            self._own = None

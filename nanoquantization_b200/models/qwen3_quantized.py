@@ -95,6 +95,14 @@ def _all_reduce(t: torch.Tensor, tp_size: int, group) -> torch.Tensor:
     return t
 
 
+def _row_parallel(linear, x: torch.Tensor, tp_size: int, group, comm) -> torch.Tensor:
+    """A row-parallel linear and its all-reduce: through the peer-memory kernel when a
+    ``PeerAllReduce`` is attached (decode-sized messages), else NCCL."""
+    if comm is not None and x.dim() == 2:
+        return comm.linear_all_reduce(linear, x)
+    return _all_reduce(linear(x), tp_size, group)
+
+
 class Qwen3QuantizedAttention(nn.Module):
     def __init__(self, hidden_size, total_num_heads, total_num_kv_heads, max_position_embeddings, w_bits=4,
                  group_size=128, head_dim=None, rope_theta=10000, rms_norm_eps=1e-6, *, tp_size=1, tp_rank=0,
@@ -114,6 +122,7 @@ class Qwen3QuantizedAttention(nn.Module):
         self.q_norm = RMSNorm(self.head_dim, rms_norm_eps)
         self.k_norm = RMSNorm(self.head_dim, rms_norm_eps)
         self.qkv_proj = None
+        self.tp_comm = None  # a PeerAllReduce, attached by attach_peer_comm()
 
     def fuse_projections(self):
         q, k, v = self.q_proj, self.k_proj, self.v_proj
@@ -166,7 +175,7 @@ class Qwen3QuantizedAttention(nn.Module):
             q, k = self.rope(q, k, positions)
         v = qkv[:, nq + nk:].view(T, self.num_kv_heads, self.head_dim)
         o = attend(q, k, v).reshape(T, nq)
-        return _all_reduce(self.o_proj(o), self.tp_size, self.tp_group)
+        return _row_parallel(self.o_proj, o, self.tp_size, self.tp_group, self.tp_comm)
 
 
 class Qwen3QuantizedMLP(nn.Module):
@@ -181,6 +190,7 @@ class Qwen3QuantizedMLP(nn.Module):
         self.gate_proj = mk(hidden_size, self.intermediate_size)
         self.down_proj = mk(self.intermediate_size, hidden_size)
         self.gate_up_proj = None
+        self.tp_comm = None
 
     def fuse_projections(self):
         g, u = self.gate_proj, self.up_proj
@@ -202,7 +212,7 @@ class Qwen3QuantizedMLP(nn.Module):
     def forward_tokens(self, x: torch.Tensor) -> torch.Tensor:
         if self.gate_up_proj is None:
             return self.forward(x)
-        return _all_reduce(self.down_proj(fused.silu_mul(self.gate_up_proj(x))), self.tp_size, self.tp_group)
+        return _row_parallel(self.down_proj, fused.silu_mul(self.gate_up_proj(x)), self.tp_size, self.tp_group, self.tp_comm)
 
 
 class Qwen3QuantizedBlock(nn.Module):
@@ -280,6 +290,12 @@ class Qwen3QuantizedForCausalLM(nn.Module):
         return cls(cfg.num_hidden_layers, cfg.vocab_size, cfg.hidden_size, cfg.total_num_heads, cfg.total_num_kv_heads,
                    cfg.max_position_embeddings, cfg.intermediate_size, cfg.w_bits, cfg.group_size, cfg.head_dim,
                    cfg.tie_word_embeddings, cfg.rope_theta, cfg.rms_norm_eps, **kw)
+
+    def attach_peer_comm(self, comm) -> None:
+        """Route the all-reduces after o_proj and down_proj through a ``PeerAllReduce``."""
+        for layer in self.model.layers:
+            layer.self_attn.tp_comm = comm
+            layer.mlp.tp_comm = comm
 
     def fuse_projections(self) -> None:
         for layer in self.model.layers:

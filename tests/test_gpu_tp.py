@@ -36,6 +36,27 @@ def _worker(rank, world, port, out):
             row = nq.RowParallelWQLinear(4, g, K, N, world, rank, dev, True, torch.float16)
             row.load_full(c["qweight"].to(dev), c["qscales"].to(dev), c["qzeros"].to(dev), c["bias"].to(dev))
             errs.append(O.rel_err(row(row.input_slice(c["x"].to(dev)).contiguous()), full))
+        # the peer-memory all-reduce: same sums as NCCL's, identical on every rank, repeatable
+        from nanoquantization_b200.layers.peer_comm import PeerAllReduce
+        comm = PeerAllReduce(slot_bytes=1 << 18, num_slots=4)
+        c = O.make_case(1024, 512, 5, group_size=128, dtype=torch.float16, seed=9)
+        row = nq.RowParallelWQLinear(4, 128, 1024, 512, world, rank, dev, False, torch.float16)
+        row.load_full(c["qweight"].to(dev), c["qscales"].to(dev), c["qzeros"].to(dev))
+        xs = row.input_slice(c["x"].to(dev)).contiguous()
+        ref_nccl = row(xs)
+        full = O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"])
+        outs = [comm.linear_all_reduce(row.shard, xs) for _ in range(11)]   # wraps the 4 slots more than twice
+        errs.append(O.rel_err(outs[-1], full))
+        same = all(torch.equal(o, outs[0]) for o in outs)
+        gathered = [torch.empty_like(outs[0]) for _ in range(world)]
+        dist.all_gather(gathered, outs[0])
+        same = same and all(torch.equal(g_, outs[0]) for g_ in gathered)
+        errs.append(0.0 if same else 1.0)
+        errs.append(float((outs[0].float() - ref_nccl.float()).abs().max() / full.abs().max()))
+        errs.append(float(comm.status()))
+        big = comm.linear_all_reduce(row.shard, torch.randn(600, 512, device=dev, dtype=torch.float16))  # too large: NCCL path
+        assert big.shape == (600, 512)
+        comm.close()
         torch.cuda.synchronize()
         out.put((rank, errs))
     finally:
