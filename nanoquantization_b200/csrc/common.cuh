@@ -48,8 +48,7 @@ int launch_umma_decode(const GemmArgs& a);
 int launch_umma_prefill(const GemmArgs& a);
 bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K);
-int launch_umma_prefill_pair(const GemmArgs& a);
-bool umma_prefill_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g);
+
 bool umma_decode_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t umma_decode_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g);

@@ -25,8 +25,12 @@
 //                 1024+z, HMUL2 applies the scale; tcgen05.st.16x128b.x2 puts
 //                 byte b into lanes 16*(b&1).. of its lane quarter of A block
 //                 b>>1.
-//   warp 1        MMA issuer: per k-step two tcgen05.mma (M=128, N=tokens,
-//                 K=16), accumulating over all of K in tensor memory.
+//   warps 1, 30   MMA issuers, one per A block: per k-step one tcgen05.mma (M=128,
+//                 N=tokens, K=16), accumulating over all of K in tensor memory.
+//                 Issuing costs the thread about 100 cycles per MMA whatever its
+//                 size (measured with in-kernel timestamps), so a single issuer
+//                 caps the tensor pipe near 60 % at N=128; two issuers on
+//                 disjoint accumulators lift that.
 //   warps 18-21   epilogue at the end of a tile: D -> registers -> bias ->
 //                 16-bit -> out[tok, n].
 //
@@ -43,7 +47,8 @@ namespace pre {
 constexpr int kTileN = 256, kTileT = 128, kUnitK = 128;
 constexpr int kStages = 4, kAStages = 2;
 constexpr int kDequantWarps = 16, kEpiWarps = 12;  // three epilogue warps per lane quarter share a tile's token columns
-constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;
+constexpr int kThreads = (2 + kDequantWarps + kEpiWarps + 1) * 32;  // + a second MMA issuer
+constexpr int kMmaWarpB = 2 + kDequantWarps + kEpiWarps;
 constexpr int kOffW = 0, kOffX0 = 16384, kOffX1 = 32768, kOffSc = 49152, kOffZ = 49664, kStageBytes = 50176;
 constexpr int kSmem = kStages * kStageBytes + 1024;
 constexpr uint32_t kStageTx = 16384 + 2 * 16384 + 512 + 128;
@@ -112,7 +117,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_afull[kAStages], bar_aempty[kAStages],
-      bar_dfull, bar_dempty, bar_drain;
+      bar_dfull, bar_dempty, bar_drain[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort_i;
 
@@ -124,11 +129,12 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int nitems = p.ntiles_n * p.ntiles_t * p.ksplit;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kDequantWarps / 2 + 1); }
-    for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&bar_afull[s]), kDequantWarps / 2); mbar_init(smem_u32(&bar_aempty[s]), 1); }
-    mbar_init(smem_u32(&bar_dfull), 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kDequantWarps / 2 + 2); }
+    for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&bar_afull[s]), kDequantWarps / 2); mbar_init(smem_u32(&bar_aempty[s]), 2); }
+    mbar_init(smem_u32(&bar_dfull), 2);
     mbar_init(smem_u32(&bar_dempty), kEpiWarps);
-    mbar_init(smem_u32(&bar_drain), 1);
+    mbar_init(smem_u32(&bar_drain[0]), 1);
+    mbar_init(smem_u32(&bar_drain[1]), 1);
     s_abort_i = 0;
     mbar_fence_init();
   }
@@ -168,9 +174,10 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int j = issued > kStages ? issued - kStages : 0; j < issued; ++j)
         mbar_wait(smem_u32(&bar_full[j % kStages]), (j / kStages) & 1);
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == kMmaWarpB) {
+    // --------------------------------------------------- MMA issuers (one per A block)
     if (lane == 0) {
+      const int blk = warp == 1 ? 0 : 1;
       const uint32_t idesc = umma_idesc(BF16 ? 1 : 0, 128, p.nt);
       int i = 0, li = 0;
       bool ok = true;
@@ -183,13 +190,12 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           if (!wait_bar(&bar_afull[sa], (i / kAStages) & 1, s_abort, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t xaddr = smem_base + s * kStageBytes + kOffX0;
-          const uint32_t a0 = tmem + kColA + sa * 128, a1 = a0 + 64, d = tmem + kColD;
+          const uint32_t a = tmem + kColA + sa * 128 + 64 * blk, d = tmem + kColD + 128 * blk;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t bdesc = umma_smem_desc_sw128(xaddr + (ks >> 2) * 16384 + (ks & 3) * 32);
             const uint32_t acc = (grp > it.g0 || ks > 0) ? 1u : 0u;
-            umma_ts(d, a0 + ks * 8, bdesc, idesc, acc);
-            umma_ts(d + 128, a1 + ks * 8, bdesc, idesc, acc);
+            umma_ts(d, a + ks * 8, bdesc, idesc, acc);
           }
           umma_commit(smem_u32(&bar_aempty[sa]));
           umma_commit(smem_u32(&bar_empty[s]));
@@ -197,8 +203,8 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
       }
       // everything issued has completed before tensor memory may be released
-      umma_commit(smem_u32(&bar_drain));
-      mbar_wait(smem_u32(&bar_drain), 0);
+      umma_commit(smem_u32(&bar_drain[blk]));
+      mbar_wait(smem_u32(&bar_drain[blk]), 0);
     }
   } else if (warp < 2 + kDequantWarps) {
     // -------------------------------------------------------------- dequantisers
@@ -257,7 +263,7 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       __syncwarp();
       if (lane == 0) { mbar_arrive(smem_u32(&bar_afull[sa])); mbar_arrive(smem_u32(&bar_empty[s])); }
     }
-  } else {
+  } else if (warp < kMmaWarpB) {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3, sub = (warp - 2 - kDequantWarps) >> 2;
     const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
