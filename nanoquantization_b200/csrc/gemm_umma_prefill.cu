@@ -368,14 +368,22 @@ bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   return M > 16 && g == 128 && K % 128 == 0 && N % 32 == 0;
 }
 
-// K is split across CTAs when the output tiles alone would leave most SMs idle.
+// K is split across CTAs when whole tiles would fill the SMs badly (few tiles, or a last wave that
+// is mostly empty): the smallest split whose work items fill at least 85 % of their waves, else the
+// best one.  The fp32 partials cost 8 * M * N bytes of L2/HBM traffic per split, hence "smallest".
 static int prefill_ksplit(int64_t M, int64_t N, int64_t K) {
   const long long tiles = ((N + pre::kTileN - 1) / pre::kTileN) * ((M + pre::kTileT - 1) / pre::kTileT);
   const int G = (int)(K / 128);
-  if (tiles * 2 > kNumSMs) return 1;
-  long long ks = kNumSMs / tiles;
-  if (ks > G) ks = G;
-  return (int)(ks < 1 ? 1 : ks);
+  int best = 1;
+  double best_eff = 0.0;
+  for (int ks = 1; ks <= 16 && ks <= G; ++ks) {
+    const long long items = tiles * ks;
+    const long long waves = (items + kNumSMs - 1) / kNumSMs;
+    const double eff = (double)items / (double)(waves * kNumSMs);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
+    if (eff >= 0.85) return ks;
+  }
+  return best;
 }
 
 size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K) {
