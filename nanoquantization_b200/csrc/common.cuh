@@ -18,6 +18,23 @@ static inline int check_launch() {
   return cudaGetLastError() == cudaSuccess ? NQB200_OK : NQB200_ERR_LAUNCH;
 }
 
+// Launch with programmatic stream serialisation: the grid may become resident while the kernel
+// before it on the stream is still finishing, and must execute grid_dependency_wait() before it
+// touches anything that kernel may write (or writes anything that kernel may read).  Read-only
+// weights can be fetched before the wait, which hides the launch and first-byte latency of
+// back-to-back layers.  Captured into a CUDA graph this becomes a programmatic dependency edge.
+template <typename... KArgs, typename... Args>
+static inline int launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  return NQB200_OK;
+}
+
 // How the split-K decode kernel tiles a problem; the same plan sizes the workspace.
 struct DecodePlan {
   int mt;        // 8-token tiles per CTA (1 or 2)
@@ -56,6 +73,12 @@ size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool decode_mma_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 
 // ---- device helpers -------------------------------------------------------
+#ifdef __CUDACC__
+// Returns once the kernel before this one on the stream has completed and its writes are visible.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream (if launched for overlap) become resident as SMs free up.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 __device__ __forceinline__ float bias_to_float(const void* bias, int bias_dtype, int n) {
   if (bias_dtype == NQB200_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n]);
   return __half2float(reinterpret_cast<const __half*>(bias)[n]);

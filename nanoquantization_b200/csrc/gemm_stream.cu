@@ -130,6 +130,9 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   }
   __syncthreads();
 
+  grid_launch_dependents();
+  if (warp != kConsumerWarps) grid_dependency_wait();  // nothing for these warps to do before the activations exist
+
   if (warp == kConsumerWarps) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
@@ -137,17 +140,36 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
       int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
       int issued = 0;
       bool ok = true;
+      // The packed weights, scales and zero-points are read-only, so the first ring of units is
+      // requested before the kernel ahead of this one on the stream has finished; the activations
+      // (its output) only after it has.
+      const int nfirst = nunits < kStages ? nunits : kStages;
+      {
+        int t2 = tile, g2 = grp;
+        for (int i = 0; i < nfirst; ++i) {
+          const uint32_t st = smem_base + i * kStageBytes, bar = smem_u32(&bar_full[i]);
+          mbar_expect_tx(bar, kStageTx);
+          tma_load_2d(st + kOffW0, &tm_w, t2 * 64, g2 * kUnitK, bar);
+          tma_load_2d(st + kOffW1, &tm_w, t2 * 64 + 32, g2 * kUnitK, bar);
+          tma_load_2d(st + kOffSc, &tm_sc, t2 * 256, g2, bar);
+          tma_load_2d(st + kOffZ, &tm_z, t2 * 64, g2, bar);
+          if (++g2 == G) { g2 = 0; ++t2; }
+        }
+      }
+      grid_dependency_wait();
       for (int i = 0; i < nunits; ++i) {
         const int s = i % kStages;
-        if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) { ok = false; break; }
         const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
-        mbar_expect_tx(bar, kStageTx);
-        tma_load_2d(st + kOffW0, &tm_w, tile * 64, grp * kUnitK, bar);
-        tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, grp * kUnitK, bar);
+        if (i >= kStages) {
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) { ok = false; break; }
+          mbar_expect_tx(bar, kStageTx);
+          tma_load_2d(st + kOffW0, &tm_w, tile * 64, grp * kUnitK, bar);
+          tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, grp * kUnitK, bar);
+          tma_load_2d(st + kOffSc, &tm_sc, tile * 256, grp, bar);
+          tma_load_2d(st + kOffZ, &tm_z, tile * 64, grp, bar);
+        }
         tma_load_2d(st + kOffX0, &tm_x, grp * kUnitK, 0, bar);
         tma_load_2d(st + kOffX1, &tm_x, grp * kUnitK + 64, 0, bar);
-        tma_load_2d(st + kOffSc, &tm_sc, tile * 256, grp, bar);
-        tma_load_2d(st + kOffZ, &tm_z, tile * 64, grp, bar);
         ++issued;
         if (++grp == G) { grp = 0; ++tile; }
       }
@@ -404,8 +426,7 @@ static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const C
     cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  stream_kernel<MT, BF16><<<sp.nctas, kStreamThreads, kStreamSmem, st>>>(tw, ts, tz, tx, sp);
-  return check_launch();
+  return launch_overlapped(stream_kernel<MT, BF16>, dim3(sp.nctas), dim3(kStreamThreads), kStreamSmem, st, tw, ts, tz, tx, sp);
 }
 
 int launch_stream(const GemmArgs& a) {

@@ -128,6 +128,8 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem;
+  grid_launch_dependents();
+  if (warp != 0) grid_dependency_wait();  // nothing for these warps to do before the activations exist
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -135,14 +137,29 @@ umma_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z); prefetch_tmap(&tm_x);
       int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
       int issued = 0;
+      // The packed weights are read-only: the first ring of them is requested before the kernel
+      // ahead of this one on the stream has finished, everything else after it has.
+      const int nfirst = nunits < kWStages ? nunits : kWStages;
+      {
+        int t2 = tile, g2 = grp;
+        for (int i = 0; i < nfirst; ++i) {
+          const uint32_t wbar = smem_u32(&bar_wfull[i]);
+          mbar_expect_tx(wbar, kWTx);
+          tma_load_2d(smem_base + i * kWStageBytes, &tm_w, t2 * 32, g2 * kUnitK, wbar);
+          if (++g2 == G) { g2 = 0; ++t2; }
+        }
+      }
+      grid_dependency_wait();
       for (int i = 0; i < nunits; ++i) {
         const int ws = i % kWStages, xs = i % kXStages;
         if (i >= kWStages && !wait_bar(&bar_wempty[ws], ((i / kWStages) - 1) & 1, s_abort, status)) break;
         if (i >= kXStages && !wait_bar(&bar_xempty[xs], ((i / kXStages) - 1) & 1, s_abort, status)) break;
         const uint32_t wst = smem_base + ws * kWStageBytes, xst = smem_base + kXRingBase + xs * kXStageBytes;
         const uint32_t wbar = smem_u32(&bar_wfull[ws]), xbar = smem_u32(&bar_xfull[xs]);
-        mbar_expect_tx(wbar, kWTx);
-        tma_load_2d(wst, &tm_w, tile * 32, grp * kUnitK, wbar);
+        if (i >= kWStages) {
+          mbar_expect_tx(wbar, kWTx);
+          tma_load_2d(wst, &tm_w, tile * 32, grp * kUnitK, wbar);
+        }
         mbar_expect_tx(xbar, kXTx);
         tma_load_2d(xst + kOffX0, &tm_x, grp * kUnitK, 0, xbar);
         tma_load_2d(xst + kOffX1, &tm_x, grp * kUnitK + 64, 0, xbar);
@@ -402,8 +419,7 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
     }
     configured = true;
   }
-  umma_decode_kernel<MC, BF16><<<sp.nctas, kThreads, kSmem, st>>>(tw, ts, tz, tx, sp);
-  return check_launch();
+  return launch_overlapped(umma_decode_kernel<MC, BF16>, dim3(sp.nctas), dim3(kThreads), kSmem, st, tw, ts, tz, tx, sp);
 }
 
 }  // namespace dec

@@ -369,21 +369,25 @@ bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
 }
 
 // K is split across CTAs when whole tiles would fill the SMs badly (few tiles, or a last wave that
-// is mostly empty): the smallest split whose work items fill at least 85 % of their waves, else the
-// best one.  The fp32 partials cost 8 * M * N bytes of L2/HBM traffic per split, hence "smallest".
+// is mostly empty).  The split is the one a small cost model of the kernel predicts to be fastest.
 static int prefill_ksplit(int64_t M, int64_t N, int64_t K) {
   const long long tiles = ((N + pre::kTileN - 1) / pre::kTileN) * ((M + pre::kTileT - 1) / pre::kTileT);
   const int G = (int)(K / 128);
+  const int nt = M >= pre::kTileT ? pre::kTileT : (int)((M + 15) / 16) * 16;
+  // measured: a CTA spends about 1.2 us on one 128-k group of a full 128-token tile (the tensor
+  // pipe), never less than 0.7 us (the dequantisers), and about 1.5 us per work item outside its
+  // group loop; a split adds a second launch and 8 bytes of fp32 traffic per output and split
+  const double t_group = 1.2 * nt / 128.0 > 0.7 ? 1.2 * nt / 128.0 : 0.7;
   int best = 1;
-  double best_eff = 0.0;
+  double best_us = 1e30, unsplit_us = 0.0;
   for (int ks = 1; ks <= 16 && ks <= G; ++ks) {
-    const long long items = tiles * ks;
-    const long long waves = (items + kNumSMs - 1) / kNumSMs;
-    const double eff = (double)items / (double)(waves * kNumSMs);
-    if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
-    if (eff >= 0.85) return ks;
+    const long long waves = (tiles * ks + kNumSMs - 1) / kNumSMs;
+    double us = (double)waves * ((double)((G + ks - 1) / ks) * t_group + 1.5);
+    if (ks > 1) us += 3.0 + (double)ks * (double)M * (double)N * 8.0 / 6.0e6;
+    if (ks == 1) unsplit_us = us;
+    if (us < best_us - 1e-9) { best_us = us; best = ks; }
   }
-  return best;
+  return best_us < 0.92 * unsplit_us ? best : 1;  // the model is good to about 10 %
 }
 
 size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K) {
