@@ -5,15 +5,18 @@
 // CTA's contiguous range of units walks down K inside a column tile.  The 148
 // CTAs take equal contiguous ranges (sizes differ by at most one unit).
 //
-//   producer warp : for each unit, six TMA tensor loads into a 5-stage
-//                   shared-memory ring (two 128x128-byte boxes of packed
-//                   weights with the 128-byte swizzle, the group's scales and
-//                   zero-points, two boxes of activations), completion on an
-//                   mbarrier.  About 190 KB per SM is in flight from the
-//                   first cycle, which is what keeps HBM busy at these sizes.
-//   sum(x) warp   : sum over the group's 128 k of every token, once per unit, into
-//                   the stage (the tensor pipe is this kernel's scarce resource, so
-//                   this is not done with an all-ones mma).
+//   producer warp : for each unit, four TMA tensor loads into a shared-memory
+//                   ring (two 128x128-byte boxes of packed weights with the
+//                   128-byte swizzle, the group's scales and zero-points),
+//                   completion on an mbarrier.  About 190 KB per SM is in flight
+//                   from the first cycle, which is what keeps HBM busy at these
+//                   sizes.  It reads nothing another kernel writes, so under
+//                   programmatic stream serialisation it starts before the
+//                   kernel ahead of it has finished.
+//   activation warp : the group's 128 k of every token by plain loads into the
+//                   stage (swizzled like a TMA tile), and their sum per token
+//                   (the tensor pipe is this kernel's scarce resource, so the sum
+//                   is not done with an all-ones mma).
 //   8 consumer warps : warp w owns columns 64w..64w+63 of the tile for the whole
 //                   group; arithmetic as in the register-fed kernel (raw nibbles
 //                   as fp16 subnormals into mma.sync m16n8k16, scale and
@@ -22,9 +25,11 @@
 //                   shared-memory load conflict-free.
 //
 // A CTA whose range covers a tile's whole K writes the output itself.  Other
-// segments go to a per-CTA slot (fp32) in the workspace; a counter per tile
-// finds the last contributor, which adds the slots in CTA order (so the result
-// does not depend on timing), adds the bias and writes the output.
+// segments go to a per-CTA slot (fp32) in the workspace, and a second, small
+// kernel adds a tile's slots in CTA order (so the result does not depend on
+// timing), adds the bias and writes the output.  Both kernels are launched with
+// programmatic stream serialisation: the second is resident before the first
+// ends, and the next layer's weights start to stream while it runs.
 //
 // Every wait is bounded; on expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in
 // the workspace status word and drains instead of spinning.
@@ -51,14 +56,15 @@ template <int MT> struct StreamCfg {
   static constexpr int kOffXs = kOffZ + 256;                  // sum over the group's k of each token, fp32
   static constexpr int kStageBytes = (kOffXs + 64 + 1023) / 1024 * 1024;
   static constexpr int kSmem = kStages * kStageBytes + 1024;
-  static constexpr int kSlotFloats = 8 * MT * kUnitN;
-  static constexpr uint32_t kStageTx = 2 * 16384 + 2 * kXBox + 1024 + 256;
+  static constexpr int kSlotFloats = 8 * MT * kUnitN;         // one segment's slot
+  static constexpr uint32_t kStageTx = 2 * 16384 + 1024 + 256;  // what TMA brings: weights, scales, zero-points
 };
 constexpr int kStatusWord = kCounterBytes / 4 - 1;  // last word of the counter region
 
 struct StreamParams {
   const void* bias; int bias_dtype; uint16_t* out;
-  int M, N, G, ntiles, nctas;
+  const uint16_t* x;
+  int M, N, K, G, ntiles, nctas;
   uint32_t U;
   int* counters; float* slots;
 };
@@ -99,8 +105,7 @@ __device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t U, uint32_t C) {
 template <int MT, bool BF16>
 __global__ void __launch_bounds__(kStreamThreads, StreamCfg<MT>::kCtasPerSm)
 stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
-              const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x,
-              const StreamParams p) {
+              const __grid_constant__ CUtensorMap tm_z, const StreamParams p) {
   constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
   constexpr float MULT_LO = BF16 ? 1.f : 16777216.f, MULT_HI = BF16 ? 1.f : 1048576.f, OFF = BF16 ? 128.f : 0.f;
   using Cfg = StreamCfg<MT>;
@@ -109,9 +114,7 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   constexpr uint32_t kStageTx = Cfg::kStageTx;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_xs[kStages], bar_seg;
-  __shared__ int s_last;
-  __shared__ int s_slot[2 * kNumSMs];  // slot of each contributor of the tile being finalised
+  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_xs[kStages];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // same place, generic pointer
@@ -125,55 +128,36 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kConsumerWarps); mbar_init(smem_u32(&bar_xs[s]), 1);
     }
-    mbar_init(smem_u32(&bar_seg), kConsumerWarps);
     mbar_fence_init();
   }
   __syncthreads();
 
   grid_launch_dependents();
-  if (warp != kConsumerWarps) grid_dependency_wait();  // nothing for these warps to do before the activations exist
+  if (warp != kConsumerWarps) grid_dependency_wait();  // all but the TMA producer touch what the kernel ahead may still write
 
   if (warp == kConsumerWarps) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z); prefetch_tmap(&tm_x);
+      prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z);
       int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
       int issued = 0;
       bool ok = true;
-      // The packed weights, scales and zero-points are read-only, so the first ring of units is
-      // requested before the kernel ahead of this one on the stream has finished; the activations
-      // (its output) only after it has.
-      const int nfirst = nunits < kStages ? nunits : kStages;
-      {
-        int t2 = tile, g2 = grp;
-        for (int i = 0; i < nfirst; ++i) {
-          const uint32_t st = smem_base + i * kStageBytes, bar = smem_u32(&bar_full[i]);
-          mbar_expect_tx(bar, kStageTx);
-          tma_load_2d(st + kOffW0, &tm_w, t2 * 64, g2 * kUnitK, bar);
-          tma_load_2d(st + kOffW1, &tm_w, t2 * 64 + 32, g2 * kUnitK, bar);
-          tma_load_2d(st + kOffSc, &tm_sc, t2 * 256, g2, bar);
-          tma_load_2d(st + kOffZ, &tm_z, t2 * 64, g2, bar);
-          if (++g2 == G) { g2 = 0; ++t2; }
-        }
-      }
-      grid_dependency_wait();
+      // Everything this thread requests (packed weights, scales, zero-points) is read-only, so it
+      // does not wait for the kernel ahead of this one on the stream; the activations come through
+      // the activation warp, which does.
       for (int i = 0; i < nunits; ++i) {
         const int s = i % kStages;
+        if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) { ok = false; break; }
         const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
-        if (i >= kStages) {
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) { ok = false; break; }
-          mbar_expect_tx(bar, kStageTx);
-          tma_load_2d(st + kOffW0, &tm_w, tile * 64, grp * kUnitK, bar);
-          tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, grp * kUnitK, bar);
-          tma_load_2d(st + kOffSc, &tm_sc, tile * 256, grp, bar);
-          tma_load_2d(st + kOffZ, &tm_z, tile * 64, grp, bar);
-        }
-        tma_load_2d(st + kOffX0, &tm_x, grp * kUnitK, 0, bar);
-        tma_load_2d(st + kOffX1, &tm_x, grp * kUnitK + 64, 0, bar);
+        mbar_expect_tx(bar, kStageTx);
+        tma_load_2d(st + kOffW0, &tm_w, tile * 64, grp * kUnitK, bar);
+        tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, grp * kUnitK, bar);
+        tma_load_2d(st + kOffSc, &tm_sc, tile * 256, grp, bar);
+        tma_load_2d(st + kOffZ, &tm_z, tile * 64, grp, bar);
         ++issued;
         if (++grp == G) { grp = 0; ++tile; }
       }
-      if (!ok) atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      if (!ok) { grid_dependency_wait(); atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); }
       // do not leave while a copy of ours may still be landing in this CTA's shared memory
       for (int i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
         mbar_wait(smem_u32(&bar_full[i % kStages]), (i / kStages) & 1);
@@ -181,27 +165,43 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     return;
   }
   if (warp == kConsumerWarps + 1) {
-    // ------------------------------------------------------------- sum(x) warp
-    // lane l adds k = 4l..4l+3 of a token's row (one 8-byte load from the swizzled tile), then a butterfly
-    const uint32_t ch = (uint32_t)(lane & 15) >> 1;
+    // --------------------------------------------------------- activation warp
+    // Brings the group's 128 k of every token from global memory with plain loads (they are small,
+    // L2-resident and must not queue behind the weight boxes), stores them in the layout of a
+    // 128-byte-swizzled tile (16-byte chunk c of row m at chunk c ^ (m & 7)), and leaves each
+    // token's sum over the group beside them.  Lanes 0-15 hold one token's 256 bytes, lanes 16-31
+    // the next token's.
+    const int cc = lane & 15, half = lane >> 4;
+    int grp = (int)(u_begin % G);
     for (int i = 0; i < nunits; ++i) {
       const int s = i % kStages;
-      if (!mbar_wait(smem_u32(&bar_full[s]), (i / kStages) & 1)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); break; }
-      uint8_t* st = const_cast<uint8_t*>(smem_gen) + s * kStageBytes;
-      const uint8_t* xb = st + ((lane >> 4) ? kOffX1 : kOffX0) + 8 * (lane & 1);
-      float mine = 0.f;
-#pragma unroll
-      for (int m = 0; m < 8 * MT; ++m) {
-        const uint2 v = *reinterpret_cast<const uint2*>(xb + m * 128 + ((ch ^ (uint32_t)(m & 7)) << 4));
-        float a = raw16_to_float<BF16>((uint16_t)(v.x & 0xFFFF)) + raw16_to_float<BF16>((uint16_t)(v.x >> 16)) +
-                  raw16_to_float<BF16>((uint16_t)(v.y & 0xFFFF)) + raw16_to_float<BF16>((uint16_t)(v.y >> 16));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
-        if (lane == m) mine = a;
+      if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) {
+        atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+        break;
       }
-      if (lane < 8 * MT) *reinterpret_cast<float*>(st + kOffXs + 4 * lane) = mine;
+      uint8_t* st = const_cast<uint8_t*>(smem_gen) + s * kStageBytes;
+      uint4 v[4 * MT];
+#pragma unroll
+      for (int j = 0; j < 4 * MT; ++j) {
+        const int m = 2 * j + half;
+        v[j] = m < p.M ? __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + grp * kUnitK) + cc) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 4 * MT; ++j) {
+        const int m = 2 * j + half;
+        *reinterpret_cast<uint4*>(st + ((cc >> 3) ? kOffX1 : kOffX0) + m * 128 + (((cc & 7) ^ (m & 7)) << 4)) = v[j];
+        const uint32_t wds[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        float a = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          a += raw16_to_float<BF16>((uint16_t)(wds[e] & 0xFFFF)) + raw16_to_float<BF16>((uint16_t)(wds[e] >> 16));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+        if (cc == 0) *reinterpret_cast<float*>(st + kOffXs + 4 * m) = a;
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_xs[s]));
+      if (++grp == G) grp = 0;
     }
     return;
   }
@@ -227,12 +227,16 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
   int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
   const int first_tile = tile;
   int seg_begin = grp;
-  uint32_t seg_phase = 0;
   bool alive = true;
 
   for (int i = 0; i < nunits && alive; ++i) {
     const int s = i % kStages;
     if (!mbar_wait(smem_u32(&bar_full[s]), (i / kStages) & 1)) {
+      atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      alive = false;
+      break;
+    }
+    if (!mbar_wait(smem_u32(&bar_xs[s]), (i / kStages) & 1)) {
       atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
       alive = false;
       break;
@@ -279,11 +283,6 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     }
 
     // scale, power of two and zero-point, once per group
-    if (!mbar_wait(smem_u32(&bar_xs[s]), (i / kStages) & 1)) {
-      atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
-      alive = false;
-      break;
-    }
     {
       float xs[MT][2];
 #pragma unroll
@@ -335,71 +334,21 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
             }
         }
       } else {
+        // rows beyond M are never read
         float* slot = p.slots + ((size_t)blockIdx.x * 2 + (tile == first_tile ? 0 : 1)) * kSlotFloats;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             const int m = 8 * mt + 2 * tig + t;
-            float* dst = slot + m * kUnitN + 64 * w + 8 * gq;  // rows beyond M are scratch inside the slot
-            __stcg(reinterpret_cast<float4*>(dst), make_float4(NQ_TOTAL_AT(total[mt], 0, t), NQ_TOTAL_AT(total[mt], 1, t),
-                                                               NQ_TOTAL_AT(total[mt], 2, t), NQ_TOTAL_AT(total[mt], 3, t)));
-            __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(NQ_TOTAL_AT(total[mt], 4, t), NQ_TOTAL_AT(total[mt], 5, t),
-                                                                   NQ_TOTAL_AT(total[mt], 6, t), NQ_TOTAL_AT(total[mt], 7, t)));
-          }
-        __threadfence();
-        // all consumer warps have published their part of the slot
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
-        if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
-        seg_phase ^= 1;
-        const int first_cta = cta_of_unit((uint32_t)tile * G, U, C);
-        const int last_cta = cta_of_unit((uint32_t)tile * G + G - 1, U, C);
-        if (threadIdx.x == 0) s_last = (atomicAdd(p.counters + tile, 1) == last_cta - first_cta);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
-        if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
-        seg_phase ^= 1;
-        if (s_last) {
-          __threadfence();
-          for (int c = first_cta + (int)threadIdx.x; c <= last_cta; c += kConsumerWarps * 32)
-            s_slot[c - first_cta] = 2 * c + ((int)(cta_begin(c, U, C) / G) == tile ? 0 : 1);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_seg));
-        if (!mbar_wait(smem_u32(&bar_seg), seg_phase)) { atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); alive = false; break; }
-        seg_phase ^= 1;
-        if (s_last) {
-          const int tn0 = tile * kUnitN;
-          const int ncontrib = last_cta - first_cta + 1;
-          for (int idx = threadIdx.x; idx < p.M * (kUnitN / 4); idx += kConsumerWarps * 32) {
-            const int m = idx / (kUnitN / 4), c4 = (idx % (kUnitN / 4)) * 4;
-            if (tn0 + c4 < p.N) {
-              const float* src = p.slots + m * kUnitN + c4;
-              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-              // loads of eight contributors are in flight together; the additions stay in CTA order
-              for (int c0 = 0; c0 < ncontrib; c0 += 8) {
-                float4 q[8];
-#pragma unroll
-                for (int d = 0; d < 8; ++d)
-                  q[d] = c0 + d < ncontrib ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)s_slot[c0 + d] * kSlotFloats))
-                                           : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int d = 0; d < 8; ++d) { v.x += q[d].x; v.y += q[d].y; v.z += q[d].z; v.w += q[d].w; }
-              }
-              if (p.bias) {
-                v.x += bias_to_float(p.bias, p.bias_dtype, tn0 + c4); v.y += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 1);
-                v.z += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 2); v.w += bias_to_float(p.bias, p.bias_dtype, tn0 + c4 + 3);
-              }
-              const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
-              const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
-              *reinterpret_cast<uint2*>(p.out + (size_t)m * p.N + tn0 + c4) = make_uint2(o0, o1);
+            if (m < p.M) {
+              float* dst = slot + m * kUnitN + 64 * w + 8 * gq;
+              __stcg(reinterpret_cast<float4*>(dst), make_float4(NQ_TOTAL_AT(total[mt], 0, t), NQ_TOTAL_AT(total[mt], 1, t),
+                                                                 NQ_TOTAL_AT(total[mt], 2, t), NQ_TOTAL_AT(total[mt], 3, t)));
+              __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(NQ_TOTAL_AT(total[mt], 4, t), NQ_TOTAL_AT(total[mt], 5, t),
+                                                                     NQ_TOTAL_AT(total[mt], 6, t), NQ_TOTAL_AT(total[mt], 7, t)));
             }
           }
-          if (threadIdx.x == 0) p.counters[tile] = 0;  // leave the workspace as it was found
-        }
-        // s_last and s_slot are next written after the first barrier round of the next segment
-        // end, which no warp can pass before every warp is done with them here
       }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -411,22 +360,87 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     }
     if (++grp == G) { grp = 0; ++tile; }
   }
+
+}
+
+// Adds the partial segments of one tile (blockIdx.x) and token (blockIdx.y).  Thread (t, j) owns
+// columns 4t..4t+3 and the contributors j, j+W, j+2W, ... (W = 1 when a tile has at most eight
+// contributors, else 4): all of a thread's loads (up to eight) are in flight together, and the W
+// partial sums of a column meet in shared memory, always in the same order, so the result does
+// not depend on timing.  Tiles that one CTA of the main kernel
+// covered alone were written there.
+template <bool BF16, int kReduceWays>
+__global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel(const StreamParams p, const int C, const int slot_floats) {
+  __shared__ float4 part[kReduceWays][kUnitN / 4];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int tile = (int)blockIdx.x, m = (int)blockIdx.y, G = p.G;
+  const int t = (int)threadIdx.x, j = (int)threadIdx.y;
+  const uint32_t U = p.U;
+  const int first_cta = cta_of_unit((uint32_t)tile * G, U, (uint32_t)C);
+  const int nc = cta_of_unit((uint32_t)tile * G + G - 1, U, (uint32_t)C) - first_cta + 1;
+  if (nc == 1) return;
+  const int col = 4 * t, n = tile * kUnitN + col;
+  // the first contributor's segment is its last one unless its range starts with this tile
+  const int first_slot = 2 * first_cta + ((int)(cta_begin(first_cta, U, (uint32_t)C) / G) == tile ? 0 : 1);
+  const float* base = p.slots + (size_t)m * kUnitN + col;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = j; c0 < nc; c0 += 8 * kReduceWays) {
+    float4 q[8];
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+      const int c = c0 + kReduceWays * d < nc ? c0 + kReduceWays * d : 0;  // beyond the last: a valid address, value unused
+      const float* src = base + (size_t)(c == 0 ? first_slot : 2 * (first_cta + c)) * slot_floats;
+      asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q[d].x), "=f"(q[d].y), "=f"(q[d].z), "=f"(q[d].w) : "l"(src));
+    }
+#pragma unroll
+    for (int d = 0; d < 8; ++d)
+      if (c0 + kReduceWays * d < nc) { v.x += q[d].x; v.y += q[d].y; v.z += q[d].z; v.w += q[d].w; }
+  }
+  part[j][t] = v;
+  __syncthreads();
+  if (j != 0 || n >= p.N) return;
+#pragma unroll
+  for (int k = 1; k < kReduceWays; ++k) { const float4 o = part[k][t]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+  if (p.bias) {
+    v.x += bias_to_float(p.bias, p.bias_dtype, n); v.y += bias_to_float(p.bias, p.bias_dtype, n + 1);
+    v.z += bias_to_float(p.bias, p.bias_dtype, n + 2); v.w += bias_to_float(p.bias, p.bias_dtype, n + 3);
+  }
+  const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
+  const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
+  *reinterpret_cast<uint2*>(p.out + (size_t)m * p.N + n) = make_uint2(o0, o1);
+}
+
+// CTAs of this kernel that one SM holds at a time (0 on error): contributors poll one another's
+// slots, so the grid must never be larger than what is resident at once.
+template <int MT, bool BF16>
+static int stream_ctas_per_sm() {
+  static int occ = -1;
+  if (occ < 0) {
+    constexpr int kStreamSmem = StreamCfg<MT>::kSmem;
+    int n = 0;
+    if (cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_kernel<MT, BF16>, kStreamThreads, kStreamSmem) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    occ = n < StreamCfg<MT>::kCtasPerSm ? n : StreamCfg<MT>::kCtasPerSm;
+  }
+  return occ;
 }
 
 template <int MT, bool BF16>
-static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx,
-                           const StreamParams& sp, cudaStream_t st) {
-  constexpr int kStreamSmem = StreamCfg<MT>::kSmem;
-  static bool configured = false;  // idempotent attribute; a repeated set from two threads is harmless
-  if (!configured) {
-    if (cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess) {
-      cudaGetLastError();
-      return NQB200_ERR_LAUNCH;
-    }
-    cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    configured = true;
-  }
-  return launch_overlapped(stream_kernel<MT, BF16>, dim3(sp.nctas), dim3(kStreamThreads), kStreamSmem, st, tw, ts, tz, tx, sp);
+static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const StreamParams& sp,
+                           int max_contributors, cudaStream_t st) {
+  // the attributes were set when the occupancy was measured
+  const int rc = launch_overlapped(stream_kernel<MT, BF16>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
+  if (rc != NQB200_OK || max_contributors <= 1) return rc;
+  if (max_contributors <= 8)
+    return launch_overlapped(stream_reduce_kernel<BF16, 1>, dim3(sp.ntiles, sp.M), dim3(kUnitN / 4, 1), 0, st, sp, sp.nctas,
+                             (int)StreamCfg<MT>::kSlotFloats);
+  return launch_overlapped(stream_reduce_kernel<BF16, 4>, dim3(sp.ntiles, sp.M), dim3(kUnitN / 4, 4), 0, st, sp, sp.nctas,
+                           (int)StreamCfg<MT>::kSlotFloats);
 }
 
 int launch_stream(const GemmArgs& a) {
@@ -435,24 +449,33 @@ int launch_stream(const GemmArgs& a) {
   const long long U = (long long)ntiles * G;
   if (U * 2 * kNumSMs >= (1ll << 31)) return NQB200_ERR_TOO_LARGE;
   const int mt = a.M > 8 ? 2 : 1;
-  const long long cap = (long long)kNumSMs * (mt == 1 ? 2 : 1);
+  const bool bf = a.dtype == NQB200_BF16;
+  const int per_sm = mt == 1 ? (bf ? stream_ctas_per_sm<1, true>() : stream_ctas_per_sm<1, false>())
+                             : (bf ? stream_ctas_per_sm<2, true>() : stream_ctas_per_sm<2, false>());
+  if (per_sm <= 0) return NQB200_ERR_LAUNCH;
+  const long long cap = (long long)kNumSMs * per_sm;
   const int C = (int)(U < cap ? U : cap);
   if (!a.ws || a.ws_bytes < stream_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
   if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
-  alignas(64) CUtensorMap tw, ts, tz, tx;
-  const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  alignas(64) CUtensorMap tw, ts, tz;
   bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
   ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, G, a.N / 2, 1, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
   ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, G, a.N / 8, 1, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
-  ok = ok && encode_2d(&tx, xdt, 2, a.x, a.M, a.K, 8 * mt, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return NQB200_ERR_LAUNCH;
   StreamParams sp;
   sp.bias = a.bias; sp.bias_dtype = a.bias_dtype; sp.out = (uint16_t*)a.out;
-  sp.M = a.M; sp.N = a.N; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = (uint32_t)U;
+  sp.x = (const uint16_t*)a.x;
+  sp.M = a.M; sp.N = a.N; sp.K = a.K; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = (uint32_t)U;
   sp.counters = (int*)a.ws; sp.slots = (float*)((char*)a.ws + kCounterBytes);
-  const bool bf = a.dtype == NQB200_BF16;
-  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, tx, sp, a.stream) : launch_stream_t<1, false>(tw, ts, tz, tx, sp, a.stream);
-  return bf ? launch_stream_t<2, true>(tw, ts, tz, tx, sp, a.stream) : launch_stream_t<2, false>(tw, ts, tz, tx, sp, a.stream);
+  // the most contributors any tile has (same arithmetic as the kernels)
+  int reduce = 1;
+  for (int t = 0; t < ntiles; ++t) {
+    const unsigned long long u0 = (unsigned long long)t * G, u1 = u0 + G - 1;
+    const int nc = (int)(((u1 + 1) * C - 1) / (unsigned long long)U - ((u0 + 1) * C - 1) / (unsigned long long)U) + 1;
+    if (nc > reduce) reduce = nc;
+  }
+  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, a.stream);
+  return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, a.stream);
 }
 
 }  // namespace nqb200
