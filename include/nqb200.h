@@ -150,7 +150,7 @@ int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int world, size_t
 int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Name of the kernel family nqb200_gemm would pick for this problem
- * ("decode_stream", "decode_tcgen05", "decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
+ * ("decode_stream", "decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
 const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
 
 #ifdef __cplusplus

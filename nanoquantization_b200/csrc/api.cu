@@ -31,12 +31,6 @@ extern "C" int nqb200_device_supported(int device) {
   return major == 10 ? 1 : 0;
 }
 
-// Up to 8 tokens the mma.sync streaming kernel is the faster decode path today; 9..16 tokens go
-// to the tcgen05 kernel, whose tensor-memory operand does not pay for the second token tile.
-static bool use_umma_decode(int64_t M, int64_t N, int64_t K, int64_t g) {
-  return M > 8 && umma_decode_supports(M, N, K, g);
-}
-
 static int check_shape(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (M < 0 || N <= 0 || K <= 0 || g <= 0 || K % g != 0 || N % 8 != 0) return NQB200_ERR_BAD_SHAPE;
   if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24)) return NQB200_ERR_TOO_LARGE;
@@ -47,7 +41,6 @@ static int check_shape(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
 extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
   if (umma_prefill_supports(M, N, K, g)) return umma_prefill_workspace_bytes(M, N, K);
-  if (use_umma_decode(M, N, K, g)) return umma_decode_workspace_bytes(M, N, K);
   if (stream_supports(M, N, K, g)) return stream_workspace_bytes(M, N, K);
   if (!decode_mma_supports(M, N, K, g)) return 0;
   const DecodePlan p = plan_decode(M, N, K, g);
@@ -57,7 +50,6 @@ extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, i
 extern "C" const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK) return "invalid";
   if (umma_prefill_supports(M, N, K, g)) return "prefill_tcgen05";
-  if (use_umma_decode(M, N, K, g)) return "decode_tcgen05";
   if (stream_supports(M, N, K, g)) return "decode_stream";
   if (!decode_mma_supports(M, N, K, g)) return "generic";
   return "decode_mma";
@@ -80,7 +72,6 @@ extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscal
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
   if (umma_prefill_supports(M, N, K, g)) return launch_umma_prefill(a);
-  if (use_umma_decode(M, N, K, g)) return launch_umma_decode(a);
   if (stream_supports(M, N, K, g)) return launch_stream(a);
   if (decode_mma_supports(M, N, K, g)) return launch_decode_mma(a);
   return launch_generic(a);

@@ -61,13 +61,10 @@ struct GemmArgs {
 int launch_decode_mma(const GemmArgs& a);
 int launch_generic(const GemmArgs& a);
 int launch_stream(const GemmArgs& a);
-int launch_umma_decode(const GemmArgs& a);
 int launch_umma_prefill(const GemmArgs& a);
 bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
-bool umma_decode_supports(int64_t M, int64_t N, int64_t K, int64_t g);
-size_t umma_decode_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool decode_mma_supports(int64_t M, int64_t N, int64_t K, int64_t g);

@@ -46,7 +46,7 @@ def test_host_only_entry_points():
     assert lib.nqb200_unpack_int4(mis, mis, 1, 1, None) == 3
     assert lib.nqb200_gemm_workspace_bytes(1, 4096, 4096, 128, 0) > 0
     assert lib.nqb200_gemm_kernel_name(1, 4096, 4096, 128, 0) in (b"decode_stream",)
-    assert lib.nqb200_gemm_kernel_name(16, 4096, 4096, 128, 0) == b"decode_tcgen05"
+    assert lib.nqb200_gemm_kernel_name(16, 4096, 4096, 128, 0) == b"decode_stream"
     assert lib.nqb200_gemm_kernel_name(1, 24, 100, 100, 0) == b"generic"
 
 
