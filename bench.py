@@ -339,7 +339,8 @@ def run_ours(args):
                        "launch": ("device-timed sweep replayed as one CUDA graph" if use_graph else "plain launches") + "; e2e through WQLinear_GEMM.forward"},
             "e2e": {"value": round(ms_e2e * 1e3 / args.steps, 2), "unit": "us", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
-            "gpu_launches": len(points) * args.steps,
+            "gpu_launches": args.steps * sum(lib.nqb200_gemm_launch_count(M, *shard_shape(*SHAPES[si], world)[::-1], GROUP, 0)
+                                             for (si, M) in points),
             "roofline": roof_prefill, "roofline_decode": roof_decode,
             "clocks": clocks, "points": per_point, "decode_qwen3_8b": decode,
         }

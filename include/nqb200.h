@@ -153,6 +153,10 @@ int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* strea
  * ("decode_stream", "decode_mma", "prefill_tcgen05", "generic"); for logs and tests. */
 const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
 
+/* Kernels one nqb200_gemm call launches for this problem: 1, or 2 when K is split across CTAs
+ * and a small second kernel adds the partial sums; 0 for an invalid or empty problem. */
+int nqb200_gemm_launch_count(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,13 @@ extern "C" const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, 
   return "decode_mma";
 }
 
+extern "C" int nqb200_gemm_launch_count(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
+  if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
+  if (umma_prefill_supports(M, N, K, g)) return umma_prefill_launches(M, N, K);
+  if (stream_supports(M, N, K, g)) return stream_launches(M, N, K);
+  return 1;
+}
+
 extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const void* qzeros,
                            const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
                            int64_t g, int dtype, void* workspace, size_t workspace_bytes, void* stream) {

@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* __rest
                                                           uint16_t* residual_out, int H, float eps) {
   extern __shared__ float hbuf[];  // H floats
   __shared__ float red[8];
+  grid_launch_dependents();  // the next kernel's weight fetch may start now
+  grid_dependency_wait();    // x and residual come from the kernel ahead
   const size_t row = (size_t)blockIdx.x * H;
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -48,6 +50,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(uint16_t* __restrict__
                                                           const int64_t* __restrict__ positions, int T, int Hq, int Hkv,
                                                           int row_stride, float eps) {
   constexpr int D = 128;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int heads = Hq + Hkv;
@@ -81,6 +85,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(uint16_t* __restrict__
 template <bool BF16>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const uint16_t* __restrict__ gate_up, uint16_t* __restrict__ out,
                                                        int64_t T, int I) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int64_t total = T * (int64_t)I;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = idx / I;
@@ -104,13 +110,9 @@ extern "C" int nqb200_add_rmsnorm(const void* x, const void* residual, const voi
   if (!x || !weight || !out) return NQB200_ERR_NULL_POINTER;
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem = (size_t)H * sizeof(float);
-  if (dtype == NQB200_BF16)
-    add_rmsnorm_kernel<true><<<(unsigned)T, 256, smem, st>>>((const uint16_t*)x, (const uint16_t*)residual, (const uint16_t*)weight,
-                                                             (uint16_t*)out, (uint16_t*)residual_out, (int)H, eps);
-  else
-    add_rmsnorm_kernel<false><<<(unsigned)T, 256, smem, st>>>((const uint16_t*)x, (const uint16_t*)residual, (const uint16_t*)weight,
-                                                              (uint16_t*)out, (uint16_t*)residual_out, (int)H, eps);
-  return check_launch();
+  return launch_overlapped(dtype == NQB200_BF16 ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>, dim3((unsigned)T), dim3(256), smem, st,
+                           (const uint16_t*)x, (const uint16_t*)residual, (const uint16_t*)weight, (uint16_t*)out,
+                           (uint16_t*)residual_out, (int)H, eps);
 }
 
 extern "C" int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
@@ -123,13 +125,9 @@ extern "C" int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k
   const int64_t warps = T * (num_q_heads + num_kv_heads);
   const unsigned blocks = (unsigned)((warps + 7) / 8);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == NQB200_BF16)
-    qknorm_rope_kernel<true><<<blocks, 256, 0, st>>>((uint16_t*)qkv, (const uint16_t*)q_weight, (const uint16_t*)k_weight, cos_sin,
-                                                     positions, (int)T, (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps);
-  else
-    qknorm_rope_kernel<false><<<blocks, 256, 0, st>>>((uint16_t*)qkv, (const uint16_t*)q_weight, (const uint16_t*)k_weight, cos_sin,
-                                                      positions, (int)T, (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps);
-  return check_launch();
+  return launch_overlapped(dtype == NQB200_BF16 ? qknorm_rope_kernel<true> : qknorm_rope_kernel<false>, dim3(blocks), dim3(256), 0, st,
+                           (uint16_t*)qkv, (const uint16_t*)q_weight, (const uint16_t*)k_weight, cos_sin, positions, (int)T,
+                           (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps);
 }
 
 extern "C" int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_t I, int dtype, void* stream) {
@@ -141,7 +139,6 @@ extern "C" int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_
   const int64_t want = (total + 255) / 256;
   const unsigned blocks = (unsigned)(want < (int64_t)kNumSMs * 16 ? want : (int64_t)kNumSMs * 16);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == NQB200_BF16) silu_mul_kernel<true><<<blocks, 256, 0, st>>>((const uint16_t*)gate_up, (uint16_t*)out, T, (int)I);
-  else silu_mul_kernel<false><<<blocks, 256, 0, st>>>((const uint16_t*)gate_up, (uint16_t*)out, T, (int)I);
-  return check_launch();
+  return launch_overlapped(dtype == NQB200_BF16 ? silu_mul_kernel<true> : silu_mul_kernel<false>, dim3(blocks), dim3(256), 0, st,
+                           (const uint16_t*)gate_up, (uint16_t*)out, T, (int)I);
 }

@@ -443,6 +443,25 @@ static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const C
                            (int)StreamCfg<MT>::kSlotFloats);
 }
 
+// the most contributors any tile has (same arithmetic as the kernels)
+static int stream_max_contributors(int ntiles, int G, int C) {
+  const unsigned long long U = (unsigned long long)ntiles * G;
+  int most = 1;
+  for (int t = 0; t < ntiles; ++t) {
+    const unsigned long long u0 = (unsigned long long)t * G, u1 = u0 + G - 1;
+    const int nc = (int)(((u1 + 1) * C - 1) / U - ((u0 + 1) * C - 1) / U) + 1;
+    if (nc > most) most = nc;
+  }
+  return most;
+}
+
+// 2 when some tile needs the reducing kernel.  Assumes the full occupancy the kernel is built for.
+int stream_launches(int64_t M, int64_t N, int64_t K) {
+  const int G = (int)(K / 128), ntiles = (int)((N + kUnitN - 1) / kUnitN);
+  const long long U = (long long)ntiles * G, cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
+  return stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap)) > 1 ? 2 : 1;
+}
+
 int launch_stream(const GemmArgs& a) {
   const int G = a.K / 128;
   const int ntiles = (a.N + kUnitN - 1) / kUnitN;
@@ -467,13 +486,7 @@ int launch_stream(const GemmArgs& a) {
   sp.x = (const uint16_t*)a.x;
   sp.M = a.M; sp.N = a.N; sp.K = a.K; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = (uint32_t)U;
   sp.counters = (int*)a.ws; sp.slots = (float*)((char*)a.ws + kCounterBytes);
-  // the most contributors any tile has (same arithmetic as the kernels)
-  int reduce = 1;
-  for (int t = 0; t < ntiles; ++t) {
-    const unsigned long long u0 = (unsigned long long)t * G, u1 = u0 + G - 1;
-    const int nc = (int)(((u1 + 1) * C - 1) / (unsigned long long)U - ((u0 + 1) * C - 1) / (unsigned long long)U) + 1;
-    if (nc > reduce) reduce = nc;
-  }
+  const int reduce = stream_max_contributors(ntiles, G, C);
   if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, a.stream);
   return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, a.stream);
 }

@@ -128,6 +128,9 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nitems = p.ntiles_n * p.ntiles_t * p.ksplit;
 
+  grid_launch_dependents();
+  grid_dependency_wait();  // the activations come from the kernel ahead on the stream
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kDequantWarps / 2 + 2); }
     for (int s = 0; s < kAStages; ++s) { mbar_init(smem_u32(&bar_afull[s]), kDequantWarps / 2); mbar_init(smem_u32(&bar_aempty[s]), 2); }
@@ -323,6 +326,8 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 template <bool BF16>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partials, const void* bias, int bias_dtype,
                                                             uint16_t* __restrict__ out, int M, int N, int ksplit) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const size_t total4 = (size_t)M * N / 4;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -352,14 +357,12 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
     }
     configured = true;
   }
-  umma_prefill_kernel<BF16><<<ctas, kThreads, kSmem, st>>>(tw, ts, tz, tx, sp);
-  if (check_launch() != NQB200_OK) return NQB200_ERR_LAUNCH;
-  if (sp.ksplit > 1) {
-    const size_t total4 = (size_t)sp.M * sp.N / 4;
-    const int blocks = (int)((total4 + 255) / 256 < (size_t)kNumSMs * 8 ? (total4 + 255) / 256 : (size_t)kNumSMs * 8);
-    splitk_reduce_kernel<BF16><<<blocks, 256, 0, st>>>(sp.partials, sp.bias, sp.bias_dtype, sp.out, sp.M, sp.N, sp.ksplit);
-  }
-  return check_launch();
+  const int rc = launch_overlapped(umma_prefill_kernel<BF16>, dim3(ctas), dim3(kThreads), kSmem, st, tw, ts, tz, tx, sp);
+  if (rc != NQB200_OK || sp.ksplit <= 1) return rc;
+  const size_t total4 = (size_t)sp.M * sp.N / 4;
+  const int blocks = (int)((total4 + 255) / 256 < (size_t)kNumSMs * 8 ? (total4 + 255) / 256 : (size_t)kNumSMs * 8);
+  return launch_overlapped(splitk_reduce_kernel<BF16>, dim3(blocks), dim3(256), 0, st, (const float*)sp.partials, sp.bias, sp.bias_dtype,
+                           sp.out, sp.M, sp.N, sp.ksplit);
 }
 
 }  // namespace pre
@@ -389,6 +392,8 @@ static int prefill_ksplit(int64_t M, int64_t N, int64_t K) {
   }
   return best_us < 0.92 * unsplit_us ? best : 1;  // the model is good to about 10 %
 }
+
+int umma_prefill_launches(int64_t M, int64_t N, int64_t K) { return prefill_ksplit(M, N, K) > 1 ? 2 : 1; }
 
 size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int ks = prefill_ksplit(M, N, K);

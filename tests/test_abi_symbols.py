@@ -48,6 +48,11 @@ def test_host_only_entry_points():
     assert lib.nqb200_gemm_kernel_name(1, 4096, 4096, 128, 0) in (b"decode_stream",)
     assert lib.nqb200_gemm_kernel_name(16, 4096, 4096, 128, 0) == b"decode_stream"
     assert lib.nqb200_gemm_kernel_name(1, 24, 100, 100, 0) == b"generic"
+    # K split across CTAs: a second kernel adds the partial sums
+    assert lib.nqb200_gemm_launch_count(1, 4096, 4096, 128, 0) == 2
+    assert lib.nqb200_gemm_launch_count(1, 512, 128, 128, 0) == 1
+    assert lib.nqb200_gemm_launch_count(4096, 4096, 4096, 128, 0) == 1
+    assert lib.nqb200_gemm_launch_count(0, 4096, 4096, 128, 0) == 0
 
 
 def test_library_is_not_older_than_its_sources():
