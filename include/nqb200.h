@@ -79,6 +79,20 @@ int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const v
                 int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* The merged gate|up projection of a Qwen3 MLP with its activation, for decode-sized M:
+ *   out[M, N/2] = silu(y[:, :N/2]) * y[:, N/2:],  y = x @ dequant(qweight, qscales, qzeros) (+ bias)
+ * with the roundings of the separate steps (y, silu(gate) and the product each rounded to the
+ * 16-bit type: models/qwen3_quantized.py:150 of the reference runs them as a linear, F.silu and a
+ * multiply).  The activation runs in the kernel that adds the split-K partial sums, so it costs no
+ * launch of its own.  Only where nqb200_gemm_gate_up_silu_supported() says 1 (M <= 16, group 128,
+ * N a multiple of 1024, K long enough that every column tile is split across CTAs); elsewhere it
+ * returns NQB200_ERR_BAD_SHAPE and the caller runs nqb200_gemm + nqb200_silu_mul.  Workspace as
+ * for nqb200_gemm with the same M, N, K. */
+int nqb200_gemm_gate_up_silu_supported(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
+int nqb200_gemm_gate_up_silu(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                             const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
+                             int64_t group_size, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* nqb200_gemm for up to 16 tokens without any device allocation by anyone.
  * It has no counterpart in the reference.  It is for callers that cannot
  * provide a scratch buffer because they cannot allocate: hosts that own all
@@ -120,6 +134,13 @@ int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, co
                        const int64_t* positions, int64_t T, int64_t num_q_heads, int64_t num_kv_heads,
                        int64_t head_dim, int64_t row_stride, float eps, int dtype, void* stream);
 int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_t I, int dtype, void* stream);
+/* nqb200_qknorm_rope that also stores the rotated k and the v of every token in a paged KV cache:
+ * k_cache and v_cache are [slots, num_kv_heads, 128] in the model dtype, slots[t] (int64) is
+ * token t's slot (block * block_size + offset).  No counterpart in the reference (it has no cache). */
+int nqb200_qknorm_rope_kv(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                          const int64_t* positions, const int64_t* slots, void* k_cache, void* v_cache, int64_t T,
+                          int64_t num_q_heads, int64_t num_kv_heads, int64_t head_dim, int64_t row_stride, float eps,
+                          int dtype, void* stream);
 
 /* One-shot all-reduce (sum) over NVLink peer memory for the small [M, N] partial results of a
  * row-parallel linear.  No counterpart in the reference (it has no distributed code).

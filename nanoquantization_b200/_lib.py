@@ -26,10 +26,13 @@ SIGNATURES = {
     "nqb200_dequant": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nqb200_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
     "nqb200_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "nqb200_gemm_gate_up_silu_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
+    "nqb200_gemm_gate_up_silu": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "nqb200_gemm_decode_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
     "nqb200_quantize_pack": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nqb200_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _int, _vp]),
     "nqb200_qknorm_rope": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _int, _vp]),
+    "nqb200_qknorm_rope_kv": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _int, _vp]),
     "nqb200_silu_mul": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "nqb200_comm_alloc": (_int, [ctypes.POINTER(_vp), _sz]),
     "nqb200_comm_free": (_int, [_vp]),

@@ -84,6 +84,32 @@ extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscal
   return launch_generic(a);
 }
 
+extern "C" int nqb200_gemm_gate_up_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
+  if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
+  return !umma_prefill_supports(M, N, K, g) && stream_silu_supported(M, N, K, g) ? 1 : 0;
+}
+
+extern "C" int nqb200_gemm_gate_up_silu(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                                        const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
+                                        int64_t g, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  const int st = check_shape(M, N, K, g, dtype);
+  if (st != NQB200_OK) return st;
+  if (M == 0) return NQB200_OK;
+  if (!nqb200_gemm_gate_up_silu_supported(M, N, K, g, dtype)) return NQB200_ERR_BAD_SHAPE;
+  if (!x || !qweight || !qscales || !qzeros || !out) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(qscales) || !aligned16(qzeros) || !aligned16(out) ||
+      (bias && !aligned16(bias)))
+    return NQB200_ERR_MISALIGNED;
+  if (bias && bias_dtype != NQB200_F16 && bias_dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  GemmArgs a;
+  a.x = x; a.qw = (const uint32_t*)qweight; a.sc = qscales; a.qz = (const uint32_t*)qzeros;
+  a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
+  a.epilogue = 1;
+  return launch_stream(a);
+}
+
 extern "C" int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace) return NQB200_ERR_NULL_POINTER;
   if (workspace_bytes < (size_t)kCounterBytes) return NQB200_ERR_WORKSPACE;

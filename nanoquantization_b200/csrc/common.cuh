@@ -56,6 +56,7 @@ struct GemmArgs {
   int dtype;
   void* ws; size_t ws_bytes;
   cudaStream_t stream;
+  int epilogue = 0;  // 1: the matrix is gate|up, out[M, N/2] = silu(gate) * up (streaming decode kernel only)
 };
 
 int launch_decode_mma(const GemmArgs& a);
@@ -68,6 +69,7 @@ size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int stream_launches(int64_t M, int64_t N, int64_t K);
+bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 int umma_prefill_launches(int64_t M, int64_t N, int64_t K);
 bool decode_mma_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 

@@ -43,21 +43,30 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint16_t* __rest
 
 // One warp per (token, head) of q and k inside a fused [T, (Hq + 2*Hkv) * D] buffer, D = 128, in place:
 // RMSNorm over the head (weight qw / kw), then the half-split rotation with the fp32 cos|sin table row
-// of the token's position.  v is untouched.
+// of the token's position.  v is untouched.  With a paged cache given ([slots, Hkv, D] for k and for v,
+// slot_of[t] = the token's slot), the rotated k and the v of every token are also stored there by
+// the warps that hold them, which saves the two scatter launches that would follow.
 template <bool BF16>
 __global__ void __launch_bounds__(256) qknorm_rope_kernel(uint16_t* __restrict__ qkv, const uint16_t* __restrict__ qw,
                                                           const uint16_t* __restrict__ kw, const float* __restrict__ cos_sin,
                                                           const int64_t* __restrict__ positions, int T, int Hq, int Hkv,
-                                                          int row_stride, float eps) {
+                                                          int row_stride, float eps, const int64_t* __restrict__ slot_of,
+                                                          uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache) {
   constexpr int D = 128;
   grid_launch_dependents();
   grid_dependency_wait();
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const int heads = Hq + Hkv;
+  const int heads = Hq + Hkv + (slot_of ? Hkv : 0);  // with a cache, the v heads get a warp each too
   if (gw >= T * heads) return;
   const int t = gw / heads, hd = gw % heads;
-  uint16_t* p = qkv + (size_t)t * row_stride + (size_t)hd * D;  // q heads first, then k heads
+  uint16_t* p = qkv + (size_t)t * row_stride + (size_t)hd * D;  // q heads first, then k heads, then v heads
+  if (hd >= Hq + Hkv) {
+    // a v head: 256 bytes to its slot
+    uint16_t* dst = v_cache + ((size_t)slot_of[t] * Hkv + (hd - Hq - Hkv)) * D;
+    reinterpret_cast<uint2*>(dst)[lane] = reinterpret_cast<const uint2*>(p)[lane];
+    return;
+  }
   const uint16_t* w = hd < Hq ? qw : kw;
   // lane owns elements lane, lane+32, lane+64, lane+96: (lane, lane+64) and (lane+32, lane+96) are rotation pairs
   float v[4];
@@ -71,13 +80,16 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(uint16_t* __restrict__
   for (int j = 0; j < 4; ++j)
     v[j] = rnd16<BF16>(rnd16<BF16>(v[j] * inv) * raw16_to_float<BF16>(w[lane + 32 * j]));
   const float* cs = cos_sin + (size_t)positions[t] * D;  // [cos(64) | sin(64)]
+  uint16_t* kdst = (slot_of && hd >= Hq) ? k_cache + ((size_t)slot_of[t] * Hkv + (hd - Hq)) * D : nullptr;
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int i = lane + 32 * j;
     const float c = cs[i], s = cs[64 + i];
     const float a = v[j], b = v[j + 2];
-    p[i] = float_to_raw16<BF16>(a * c - b * s);
-    p[i + 64] = float_to_raw16<BF16>(a * s + b * c);
+    const uint16_t lo = float_to_raw16<BF16>(a * c - b * s), hi = float_to_raw16<BF16>(a * s + b * c);
+    p[i] = lo;
+    p[i + 64] = hi;
+    if (kdst) { kdst[i] = lo; kdst[i + 64] = hi; }
   }
 }
 
@@ -115,19 +127,37 @@ extern "C" int nqb200_add_rmsnorm(const void* x, const void* residual, const voi
                            (uint16_t*)residual_out, (int)H, eps);
 }
 
-extern "C" int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
-                                  const int64_t* positions, int64_t T, int64_t num_q_heads, int64_t num_kv_heads,
-                                  int64_t head_dim, int64_t row_stride, float eps, int dtype, void* stream) {
+static int qknorm_rope_launch(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                              const int64_t* positions, const int64_t* slots, void* k_cache, void* v_cache, int64_t T,
+                              int64_t num_q_heads, int64_t num_kv_heads, int64_t head_dim, int64_t row_stride, float eps,
+                              int dtype, void* stream) {
   if (T < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim != 128) return NQB200_ERR_BAD_SHAPE;
   if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
   if (T == 0) return NQB200_OK;
   if (!qkv || !q_weight || !k_weight || !cos_sin || !positions) return NQB200_ERR_NULL_POINTER;
-  const int64_t warps = T * (num_q_heads + num_kv_heads);
+  if (slots && (!k_cache || !v_cache)) return NQB200_ERR_NULL_POINTER;
+  const int64_t warps = T * (num_q_heads + num_kv_heads + (slots ? num_kv_heads : 0));
   const unsigned blocks = (unsigned)((warps + 7) / 8);
   cudaStream_t st = (cudaStream_t)stream;
   return launch_overlapped(dtype == NQB200_BF16 ? qknorm_rope_kernel<true> : qknorm_rope_kernel<false>, dim3(blocks), dim3(256), 0, st,
                            (uint16_t*)qkv, (const uint16_t*)q_weight, (const uint16_t*)k_weight, cos_sin, positions, (int)T,
-                           (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps);
+                           (int)num_q_heads, (int)num_kv_heads, (int)row_stride, eps, slots, (uint16_t*)k_cache, (uint16_t*)v_cache);
+}
+
+extern "C" int nqb200_qknorm_rope(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                                  const int64_t* positions, int64_t T, int64_t num_q_heads, int64_t num_kv_heads,
+                                  int64_t head_dim, int64_t row_stride, float eps, int dtype, void* stream) {
+  return qknorm_rope_launch(qkv, q_weight, k_weight, cos_sin, positions, nullptr, nullptr, nullptr, T, num_q_heads, num_kv_heads,
+                            head_dim, row_stride, eps, dtype, stream);
+}
+
+extern "C" int nqb200_qknorm_rope_kv(void* qkv, const void* q_weight, const void* k_weight, const float* cos_sin,
+                                     const int64_t* positions, const int64_t* slots, void* k_cache, void* v_cache, int64_t T,
+                                     int64_t num_q_heads, int64_t num_kv_heads, int64_t head_dim, int64_t row_stride, float eps,
+                                     int dtype, void* stream) {
+  if (!slots) return NQB200_ERR_NULL_POINTER;
+  return qknorm_rope_launch(qkv, q_weight, k_weight, cos_sin, positions, slots, k_cache, v_cache, T, num_q_heads, num_kv_heads,
+                            head_dim, row_stride, eps, dtype, stream);
 }
 
 extern "C" int nqb200_silu_mul(const void* gate_up, void* out, int64_t T, int64_t I, int dtype, void* stream) {

@@ -363,28 +363,21 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
 
 }
 
-// Adds the partial segments of one tile (blockIdx.x) and token (blockIdx.y).  Thread (t, j) owns
-// columns 4t..4t+3 and the contributors j, j+W, j+2W, ... (W = 1 when a tile has at most eight
-// contributors, else 4): all of a thread's loads (up to eight) are in flight together, and the W
-// partial sums of a column meet in shared memory, always in the same order, so the result does
-// not depend on timing.  Tiles that one CTA of the main kernel
-// covered alone were written there.
-template <bool BF16, int kReduceWays>
-__global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel(const StreamParams p, const int C, const int slot_floats) {
-  __shared__ float4 part[kReduceWays][kUnitN / 4];
-  grid_launch_dependents();
-  grid_dependency_wait();
-  const int tile = (int)blockIdx.x, m = (int)blockIdx.y, G = p.G;
-  const int t = (int)threadIdx.x, j = (int)threadIdx.y;
+// Sum over the contributors j, j+W, j+2W, ... of one tile's partial segments for token m, columns
+// col..col+3: all of a thread's loads (up to eight) are in flight together.  Returns the number of
+// contributors of the tile.
+template <int kReduceWays>
+__device__ __forceinline__ int reduce_tile_partials(const StreamParams& p, int C, int slot_floats, int tile, int m, int col, int j,
+                                                    float4& v) {
+  const int G = p.G;
   const uint32_t U = p.U;
   const int first_cta = cta_of_unit((uint32_t)tile * G, U, (uint32_t)C);
   const int nc = cta_of_unit((uint32_t)tile * G + G - 1, U, (uint32_t)C) - first_cta + 1;
-  if (nc == 1) return;
-  const int col = 4 * t, n = tile * kUnitN + col;
   // the first contributor's segment is its last one unless its range starts with this tile
   const int first_slot = 2 * first_cta + ((int)(cta_begin(first_cta, U, (uint32_t)C) / G) == tile ? 0 : 1);
   const float* base = p.slots + (size_t)m * kUnitN + col;
-  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (nc == 1) return 1;
   for (int c0 = j; c0 < nc; c0 += 8 * kReduceWays) {
     float4 q[8];
 #pragma unroll
@@ -397,22 +390,67 @@ __global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel
     for (int d = 0; d < 8; ++d)
       if (c0 + kReduceWays * d < nc) { v.x += q[d].x; v.y += q[d].y; v.z += q[d].z; v.w += q[d].w; }
   }
-  part[j][t] = v;
+  return nc;
+}
+
+// Adds the partial segments of one tile (blockIdx.x) and token (blockIdx.y).  Thread (t, j) owns
+// columns 4t..4t+3 and the contributors j, j+W, j+2W, ... (W = 1 when a tile has at most eight
+// contributors, else 4); the W partial sums of a column meet in shared memory, always in the same
+// order, so the result does not depend on timing.  Tiles that one CTA of the main kernel covered
+// alone were written there.
+//
+// SILU: the matrix is a merged gate|up projection (N = 2 I).  The CTA adds tile blockIdx.x of the
+// gate half and the same tile of the up half and writes silu(gate) * up to out[M, I], with the
+// roundings of the separate steps (each half to 16 bits, silu to 16 bits, the product to 16 bits:
+// models/qwen3_quantized.py:150 of the reference).  The host takes this path only when every tile
+// has more than one contributor.
+template <bool BF16, int kReduceWays, bool SILU>
+__global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel(const StreamParams p, const int C, const int slot_floats) {
+  __shared__ float4 part[SILU ? 2 : 1][kReduceWays][kUnitN / 4];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int tile = (int)blockIdx.x, m = (int)blockIdx.y;
+  const int t = (int)threadIdx.x, j = (int)threadIdx.y;
+  const int col = 4 * t, n = tile * kUnitN + col;
+  float4 v, u = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int nc = reduce_tile_partials<kReduceWays>(p, C, slot_floats, tile, m, col, j, v);
+  if (!SILU && nc == 1) return;
+  const int half_n = p.N / 2;
+  if (SILU) reduce_tile_partials<kReduceWays>(p, C, slot_floats, tile + p.ntiles / 2, m, col, j, u);
+  part[0][j][t] = v;
+  if (SILU) part[SILU ? 1 : 0][j][t] = u;
   __syncthreads();
-  if (j != 0 || n >= p.N) return;
+  if (j != 0 || n >= (SILU ? half_n : p.N)) return;
 #pragma unroll
-  for (int k = 1; k < kReduceWays; ++k) { const float4 o = part[k][t]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+  for (int k = 1; k < kReduceWays; ++k) {
+    const float4 o = part[0][k][t];
+    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+    if (SILU) { const float4 o2 = part[SILU ? 1 : 0][k][t]; u.x += o2.x; u.y += o2.y; u.z += o2.z; u.w += o2.w; }
+  }
   if (p.bias) {
     v.x += bias_to_float(p.bias, p.bias_dtype, n); v.y += bias_to_float(p.bias, p.bias_dtype, n + 1);
     v.z += bias_to_float(p.bias, p.bias_dtype, n + 2); v.w += bias_to_float(p.bias, p.bias_dtype, n + 3);
+    if (SILU) {
+      u.x += bias_to_float(p.bias, p.bias_dtype, half_n + n); u.y += bias_to_float(p.bias, p.bias_dtype, half_n + n + 1);
+      u.z += bias_to_float(p.bias, p.bias_dtype, half_n + n + 2); u.w += bias_to_float(p.bias, p.bias_dtype, half_n + n + 3);
+    }
+  }
+  if (SILU) {
+    auto act = [](float g, float up) {
+      g = raw16_to_float<BF16>(float_to_raw16<BF16>(g));
+      up = raw16_to_float<BF16>(float_to_raw16<BF16>(up));
+      const float sl = raw16_to_float<BF16>(float_to_raw16<BF16>(g / (1.f + expf(-g))));
+      return sl * up;
+    };
+    v.x = act(v.x, u.x); v.y = act(v.y, u.y); v.z = act(v.z, u.z); v.w = act(v.w, u.w);
   }
   const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
   const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
-  *reinterpret_cast<uint2*>(p.out + (size_t)m * p.N + n) = make_uint2(o0, o1);
+  *reinterpret_cast<uint2*>(p.out + (size_t)m * (SILU ? half_n : p.N) + n) = make_uint2(o0, o1);
 }
 
-// CTAs of this kernel that one SM holds at a time (0 on error): contributors poll one another's
-// slots, so the grid must never be larger than what is resident at once.
+// CTAs of this kernel that one SM holds at a time (0 on error): the persistent grid is sized so
+// that all of it is resident at once.
 template <int MT, bool BF16>
 static int stream_ctas_per_sm() {
   static int occ = -1;
@@ -432,27 +470,43 @@ static int stream_ctas_per_sm() {
 
 template <int MT, bool BF16>
 static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const StreamParams& sp,
-                           int max_contributors, cudaStream_t st) {
+                           int max_contributors, bool silu, cudaStream_t st) {
   // the attributes were set when the occupancy was measured
   const int rc = launch_overlapped(stream_kernel<MT, BF16>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
   if (rc != NQB200_OK || max_contributors <= 1) return rc;
+  const int sf = (int)StreamCfg<MT>::kSlotFloats;
+  const dim3 grid(silu ? sp.ntiles / 2 : sp.ntiles, sp.M);
   if (max_contributors <= 8)
-    return launch_overlapped(stream_reduce_kernel<BF16, 1>, dim3(sp.ntiles, sp.M), dim3(kUnitN / 4, 1), 0, st, sp, sp.nctas,
-                             (int)StreamCfg<MT>::kSlotFloats);
-  return launch_overlapped(stream_reduce_kernel<BF16, 4>, dim3(sp.ntiles, sp.M), dim3(kUnitN / 4, 4), 0, st, sp, sp.nctas,
-                           (int)StreamCfg<MT>::kSlotFloats);
+    return silu ? launch_overlapped(stream_reduce_kernel<BF16, 1, true>, grid, dim3(kUnitN / 4, 1), 0, st, sp, sp.nctas, sf)
+                : launch_overlapped(stream_reduce_kernel<BF16, 1, false>, grid, dim3(kUnitN / 4, 1), 0, st, sp, sp.nctas, sf);
+  return silu ? launch_overlapped(stream_reduce_kernel<BF16, 4, true>, grid, dim3(kUnitN / 4, 4), 0, st, sp, sp.nctas, sf)
+              : launch_overlapped(stream_reduce_kernel<BF16, 4, false>, grid, dim3(kUnitN / 4, 4), 0, st, sp, sp.nctas, sf);
 }
 
 // the most contributors any tile has (same arithmetic as the kernels)
-static int stream_max_contributors(int ntiles, int G, int C) {
+static int stream_max_contributors(int ntiles, int G, int C, int* fewest = nullptr) {
   const unsigned long long U = (unsigned long long)ntiles * G;
-  int most = 1;
+  int most = 1, least = 1 << 30;
   for (int t = 0; t < ntiles; ++t) {
     const unsigned long long u0 = (unsigned long long)t * G, u1 = u0 + G - 1;
     const int nc = (int)(((u1 + 1) * C - 1) / U - ((u0 + 1) * C - 1) / U) + 1;
     if (nc > most) most = nc;
+    if (nc < least) least = nc;
   }
+  if (fewest) *fewest = least;
   return most;
+}
+
+// The merged gate|up epilogue needs both halves tile-aligned and every tile reduced by the second
+// kernel (a tile that one CTA covers alone is written by the main kernel, before the activation).
+// Assumes the full occupancy the kernel is built for; launch_stream checks again with the real one.
+bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
+  if (!stream_supports(M, N, K, g) || N % (2 * kUnitN) != 0) return false;
+  const int G = (int)(K / 128), ntiles = (int)(N / kUnitN);
+  const long long U = (long long)ntiles * G, cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
+  int fewest = 0;
+  stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap), &fewest);
+  return fewest >= 2;
 }
 
 // 2 when some tile needs the reducing kernel.  Assumes the full occupancy the kernel is built for.
@@ -486,9 +540,12 @@ int launch_stream(const GemmArgs& a) {
   sp.x = (const uint16_t*)a.x;
   sp.M = a.M; sp.N = a.N; sp.K = a.K; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = (uint32_t)U;
   sp.counters = (int*)a.ws; sp.slots = (float*)((char*)a.ws + kCounterBytes);
-  const int reduce = stream_max_contributors(ntiles, G, C);
-  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, a.stream);
-  return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, a.stream);
+  int fewest = 0;
+  const int reduce = stream_max_contributors(ntiles, G, C, &fewest);
+  const bool silu = a.epilogue == 1;
+  if (silu && (a.N % (2 * kUnitN) != 0 || fewest < 2)) return NQB200_ERR_BAD_SHAPE;
+  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, silu, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, silu, a.stream);
+  return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, silu, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, silu, a.stream);
 }
 
 }  // namespace nqb200

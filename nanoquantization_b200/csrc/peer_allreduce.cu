@@ -52,6 +52,8 @@ __device__ __forceinline__ uint4 ld_peer(const uint4* p) {
 
 template <bool BF16>
 __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const ArParams p) {
+  grid_launch_dependents();
+  grid_dependency_wait();  // our slot was filled by the kernel ahead on the stream
   uint8_t* mine = p.peers[p.rank];
   uint32_t* my_epoch = reinterpret_cast<uint32_t*>(mine + kArOffEpoch) + blockIdx.x;
   __shared__ uint32_t s_epoch;
@@ -149,7 +151,6 @@ extern "C" int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int wo
   p.n = M * N; p.N = (int)N;
   cudaStream_t st = (cudaStream_t)stream;
   // always the same number of CTAs: each CTA has its own flags and call counter
-  if (dtype == NQB200_BF16) peer_allreduce_kernel<true><<<kArBlocks, kArThreads, 0, st>>>(p);
-  else peer_allreduce_kernel<false><<<kArBlocks, kArThreads, 0, st>>>(p);
-  return check_launch();
+  return launch_overlapped(dtype == NQB200_BF16 ? peer_allreduce_kernel<true> : peer_allreduce_kernel<false>, dim3(kArBlocks),
+                           dim3(kArThreads), 0, st, p);
 }

@@ -170,8 +170,9 @@ class LLMEngine:
             return None
 
     def _prefill_attend(self, layer: int, slots: torch.Tensor, lens: list[int]) -> Callable:
-        def attend(q, k, v):
-            self.cache.write(layer, slots, k, v)
+        def attend(q, k, v, stored=False):
+            if not stored:
+                self.cache.write(layer, slots, k, v)
             outs, o = [], 0
             for n in lens:
                 qs, ks, vs = (t[o:o + n].transpose(0, 1).unsqueeze(0) for t in (q, k, v))
@@ -179,12 +180,14 @@ class LLMEngine:
                                                            enable_gqa=self.q_heads != self.kv_heads)[0].transpose(0, 1))
                 o += n
             return torch.cat(outs, dim=0)
+        attend.kv_target = (self.cache.k[layer], self.cache.v[layer], slots)
         return attend
 
     def _decode_attend(self, layer: int, slots: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor,
                        max_blocks: int, ctx_i32=None, bt_i32=None) -> Callable:
-        def attend(q, k, v):
-            self.cache.write(layer, slots, k, v)
+        def attend(q, k, v, stored=False):
+            if not stored:
+                self.cache.write(layer, slots, k, v)
             B = q.shape[0]
             if self.paged_attention is not None:
                 return self.paged_attention(q.unsqueeze(1), self.cache.k[layer], self.cache.v[layer],
@@ -196,6 +199,7 @@ class LLMEngine:
             o = F.scaled_dot_product_attention(q.unsqueeze(2), kk.transpose(1, 2), vv.transpose(1, 2),
                                                attn_mask=mask[:, None, None, :], enable_gqa=self.q_heads != self.kv_heads)
             return o.squeeze(2)
+        attend.kv_target = (self.cache.k[layer], self.cache.v[layer], slots)
         return attend
 
     # --------------------------------------------------------------------- steps

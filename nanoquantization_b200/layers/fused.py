@@ -25,11 +25,24 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Te
 
 
 def qknorm_rope_(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, cos_sin: torch.Tensor,
-                 positions: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float) -> torch.Tensor:
-    """In place on ``qkv [T, (Hq + 2 Hkv) * D]``: per-head RMSNorm of q and k, then rotary embedding."""
+                 positions: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, eps: float,
+                 kv_target=None) -> torch.Tensor:
+    """In place on ``qkv [T, (Hq + 2 Hkv) * D]``: per-head RMSNorm of q and k, then rotary embedding.
+    ``kv_target = (k_cache, v_cache, slots)``: also store the rotated k and v of token t in row
+    ``slots[t]`` of the caches (each ``[..., Hkv, D]`` contiguous, any leading shape)."""
     _lib.require_cuda(qkv, q_weight, k_weight, cos_sin, positions)
     assert qkv.is_contiguous() and positions.dtype == torch.int64 and cos_sin.dtype == torch.float32
     T = qkv.shape[0]
+    if kv_target is not None:
+        k_cache, v_cache, slots = kv_target
+        _lib.require_cuda(k_cache, v_cache, slots)
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and slots.dtype == torch.int64 and slots.numel() == T
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype and k_cache.shape[-2:] == (num_kv_heads, head_dim)
+        _lib.check(_lib.load().nqb200_qknorm_rope_kv(qkv.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(), cos_sin.data_ptr(),
+                                                     positions.data_ptr(), slots.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                     T, num_q_heads, num_kv_heads, head_dim, qkv.shape[1], float(eps),
+                                                     _lib.dtype_code(qkv.dtype), _lib.stream_ptr()))
+        return qkv
     _lib.check(_lib.load().nqb200_qknorm_rope(qkv.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr(), cos_sin.data_ptr(),
                                               positions.data_ptr(), T, num_q_heads, num_kv_heads, head_dim, qkv.shape[1],
                                               float(eps), _lib.dtype_code(qkv.dtype), _lib.stream_ptr()))

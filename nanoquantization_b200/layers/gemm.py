@@ -82,9 +82,12 @@ _ws_bytes_cache: dict[tuple, int] = {}
 
 
 def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros: torch.Tensor,
-           bias: torch.Tensor | None, out: torch.Tensor | None = None) -> torch.Tensor:
+           bias: torch.Tensor | None, out: torch.Tensor | None = None, silu_mul: bool = False) -> torch.Tensor:
     """One fused call: out = x @ ((q - z) * s) (+ bias), any M.  ``out`` may name a preallocated
-    contiguous ``[M, N]`` tensor of the output dtype (e.g. a slot of a peer-mapped buffer)."""
+    contiguous ``[M, N]`` tensor of the output dtype (e.g. a slot of a peer-mapped buffer).
+    ``silu_mul``: the matrix is a merged gate|up projection and the result is
+    ``silu(y[:, :N/2]) * y[:, N/2:]`` (``[M, N/2]``); the caller has checked that the library
+    supports it for this shape."""
     M, K = x.shape
     N = qweight.shape[1] * 8
     group_size = K // qscales.shape[0]
@@ -99,13 +102,15 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
     if bias is not None:
         bias = _contig(bias)
         bias_ptr, bias_code = bias.data_ptr(), _lib.dtype_code(bias.dtype)
+    n_out = N // 2 if silu_mul else N
     if out is None:
-        out = torch.empty(M, N, dtype=dtype, device=dev)
+        out = torch.empty(M, n_out, dtype=dtype, device=dev)
     else:
-        assert out.shape == (M, N) and out.dtype == dtype and out.is_contiguous()
+        assert out.shape == (M, n_out) and out.dtype == dtype and out.is_contiguous()
     if M == 0:
         return out
     lib = _lib.load()
+    entry = lib.nqb200_gemm_gate_up_silu if silu_mul else lib.nqb200_gemm
     key = (M, N, K, group_size, code)
     nbytes = _ws_bytes_cache.get(key)
     if nbytes is None:
@@ -116,10 +121,10 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
         torch.cuda.set_device(dev)
     try:
         ws = _lib.workspace(dev, nbytes)
-        status = lib.nqb200_gemm(x.data_ptr(), qweight.data_ptr(), qscales.data_ptr(), qzeros.data_ptr(),
-                                 bias_ptr, bias_code, out.data_ptr(), M, N, K, group_size, code,
-                                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-                                 _lib.stream_ptr())
+        status = entry(x.data_ptr(), qweight.data_ptr(), qscales.data_ptr(), qzeros.data_ptr(),
+                       bias_ptr, bias_code, out.data_ptr(), M, N, K, group_size, code,
+                       ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                       _lib.stream_ptr())
     finally:
         if other_device:
             torch.cuda.set_device(prev)
@@ -276,6 +281,22 @@ class WQLinear_GEMM(nn.Module):
         x = x.reshape(-1, x.shape[-1])
         out = _w4a16(x, self.qweight, self.qscales, self.qzeros, self.bias, out)
         return out.reshape(out_shape)
+
+    @torch.no_grad()
+    def forward_silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+        """For a merged gate|up projection: ``silu(y[..., :N/2]) * y[..., N/2:]`` with ``y = forward(x)``,
+        bit-identical to running the three steps one after the other.  For decode-sized inputs the
+        activation runs inside the kernel that finishes the GEMM; otherwise as a launch of its own."""
+        from . import fused
+        x2 = x.reshape(-1, x.shape[-1])
+        M, K = x2.shape
+        lib = _lib.load()
+        if x2.is_cuda and M > 0 and lib.nqb200_gemm_gate_up_silu_supported(M, self.out_features, K, self.group_size,
+                                                                             _lib.dtype_code(self.qscales.dtype)):
+            out = _w4a16(x2, self.qweight, self.qscales, self.qzeros, self.bias, None, silu_mul=True)
+        else:
+            out = fused.silu_mul(_w4a16(x2, self.qweight, self.qscales, self.qzeros, self.bias, None))
+        return out.reshape(x.shape[:-1] + (self.out_features // 2,))
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, "

@@ -156,7 +156,8 @@ class Qwen3QuantizedAttention(nn.Module):
         return _all_reduce(self.o_proj(o), self.tp_size, self.tp_group)
 
     def forward_tokens(self, x: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
-        """``x`` is ``[T, hidden]``; ``attend(q, k, v)`` stores k, v in its cache and returns ``[T, Hq, D]``.
+        """``x`` is ``[T, hidden]``; ``attend(q, k, v)`` stores k, v in its cache and returns ``[T, Hq, D]``
+        (called with ``stored=True`` when this method already stored them through ``attend.kv_target``).
         One launch for q/k/v (when fused), one for QK-norm + rotary embedding."""
         T = x.shape[0]
         nq, nk = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
@@ -164,9 +165,13 @@ class Qwen3QuantizedAttention(nn.Module):
             qkv = self.qkv_proj(x)
         else:
             qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], dim=-1)
+        stored = False
         if self.head_dim == 128:
+            # an attend() that exposes its cache (k_cache, v_cache, slots) gets k and v stored by this launch
+            kv_target = getattr(attend, "kv_target", None)
             fused.qknorm_rope_(qkv, self.q_norm.weight, self.k_norm.weight, self.rope.cos_sin_cache, positions,
-                               self.num_heads, self.num_kv_heads, self.head_dim, self.q_norm.eps)
+                               self.num_heads, self.num_kv_heads, self.head_dim, self.q_norm.eps, kv_target)
+            stored = kv_target is not None
             q = qkv[:, :nq].view(T, self.num_heads, self.head_dim)
             k = qkv[:, nq:nq + nk].view(T, self.num_kv_heads, self.head_dim)
         else:
@@ -174,7 +179,7 @@ class Qwen3QuantizedAttention(nn.Module):
             k = self.k_norm(qkv[:, nq:nq + nk].reshape(T, self.num_kv_heads, self.head_dim))
             q, k = self.rope(q, k, positions)
         v = qkv[:, nq + nk:].view(T, self.num_kv_heads, self.head_dim)
-        o = attend(q, k, v).reshape(T, nq)
+        o = (attend(q, k, v, stored=True) if stored else attend(q, k, v)).reshape(T, nq)
         return _row_parallel(self.o_proj, o, self.tp_size, self.tp_group, self.tp_comm)
 
 
@@ -212,7 +217,7 @@ class Qwen3QuantizedMLP(nn.Module):
     def forward_tokens(self, x: torch.Tensor) -> torch.Tensor:
         if self.gate_up_proj is None:
             return self.forward(x)
-        return _row_parallel(self.down_proj, fused.silu_mul(self.gate_up_proj(x)), self.tp_size, self.tp_group, self.tp_comm)
+        return _row_parallel(self.down_proj, self.gate_up_proj.forward_silu_mul(x), self.tp_size, self.tp_group, self.tp_comm)
 
 
 class Qwen3QuantizedBlock(nn.Module):

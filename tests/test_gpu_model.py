@@ -111,3 +111,48 @@ def test_fused_kernels_match_reference_modules(dtype):
 
     gu = torch.randn(T, 2 * I, generator=g, device=DEV).to(dtype)
     assert close(fused.silu_mul(gu), torch.nn.functional.silu(gu[:, :I]) * gu[:, I:])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@torch.no_grad()
+def test_qknorm_rope_stores_k_and_v_in_the_paged_cache(dtype):
+    """The cache rows written by the fused launch equal the in-place result scattered with index_copy_."""
+    from nanoquantization_b200.layers import fused
+    from nanoquantization_b200.models import RotaryCache
+    g = torch.Generator(device=DEV).manual_seed(9)
+    T, Hq, Hkv, D, blocks, bs = 5, 4, 2, 128, 6, 16
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g, device=DEV).to(dtype)
+    qw = (torch.rand(D, generator=g, device=DEV) + 0.5).to(dtype)
+    kw = (torch.rand(D, generator=g, device=DEV) + 0.5).to(dtype)
+    rope = RotaryCache(D, 4096, 1e6).to(DEV)
+    pos = torch.tensor([3, 0, 77, 4095, 12], device=DEV)
+    slots = torch.tensor([17, 0, 95, 33, 64], device=DEV)
+    plain = qkv.clone()
+    fused.qknorm_rope_(plain, qw, kw, rope.cos_sin_cache, pos, Hq, Hkv, D, 1e-6)
+    kc = torch.full((blocks, bs, Hkv, D), 7.0, dtype=dtype, device=DEV)
+    vc = torch.full((blocks, bs, Hkv, D), 7.0, dtype=dtype, device=DEV)
+    fused.qknorm_rope_(qkv, qw, kw, rope.cos_sin_cache, pos, Hq, Hkv, D, 1e-6, (kc, vc, slots))
+    assert torch.equal(qkv, plain)
+    want_k = torch.full_like(kc, 7.0).view(-1, Hkv, D).index_copy_(0, slots, plain[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D))
+    want_v = torch.full_like(vc, 7.0).view(-1, Hkv, D).index_copy_(0, slots, plain[:, (Hq + Hkv) * D:].reshape(T, Hkv, D))
+    assert torch.equal(kc.view(-1, Hkv, D), want_k) and torch.equal(vc.view(-1, Hkv, D), want_v)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("K,I,M", [(2048, 6144, 1), (2048, 6144, 16), (1024, 1536, 4), (5120, 3200, 3), (256, 512, 2), (4096, 1024, 64)])
+@torch.no_grad()
+def test_gate_up_with_fused_activation_is_bit_identical_to_the_separate_steps(K, I, M, dtype):
+    """forward_silu_mul == silu_mul(forward(x)) bit for bit, on shapes that take the fused epilogue
+    (decode sizes, I a multiple of 512, K split across CTAs) and on shapes that fall back."""
+    from nanoquantization_b200.layers import fused
+    import oracle.awq_oracle as O
+    host = O.make_case(K, 2 * I, M, group_size=128, dtype=dtype, seed=21, bias=(M == 4))
+    lin = nq.WQLinear_GEMM(4, 128, K, 2 * I, DEV, host["bias"] is not None, dtype)
+    lin.qweight.copy_(host["qweight"]); lin.qscales.copy_(host["qscales"]); lin.qzeros.copy_(host["qzeros"])
+    if host["bias"] is not None:
+        lin.bias.copy_(host["bias"])
+    x = host["x"].to(DEV)
+    want = fused.silu_mul(lin(x))
+    got = lin.forward_silu_mul(x)
+    assert got.shape == (M, I) and torch.equal(got, want)
+    assert torch.equal(lin.forward_silu_mul(x), want)  # and again: the workspace is left reusable
