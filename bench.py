@@ -383,6 +383,8 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
     per_seq = -(-(context + steps + 8) // block)
     eng = LLMEngine(model, num_blocks=max(batches) * per_seq + 4, block_size=block, max_batch=max(batches))
     out = {"model": "qwen3-8b-arch w4 g128 random init", "tp": world, "context": context,
+           "allreduce_variants": "nccl = NCCL after each row-parallel linear; peer = nqb200_gemm_allreduce "
+                                 "(reduced over peer memory by the kernel that finishes the GEMM)",
            "attention": "flash_attn paged" if eng.paged_attention is not None else "sdpa over gathered pages", "points": []}
     g = torch.Generator().manual_seed(1)
     comm = None

@@ -160,6 +160,22 @@ int nqb200_comm_export(void* ptr, void* handle64);
 int nqb200_comm_import(const void* handle64, void** ptr);
 int nqb200_comm_unimport(void* ptr);
 size_t nqb200_comm_data_offset(void);
+/* A row-parallel linear and its all-reduce in one call, for decode-sized M: every rank calls it with
+ * its shard (x [M, K/world], weights [K/world, N]); the kernel that finishes the GEMM stores the
+ * rank's partial result (rounded to the 16-bit type) straight into the slot at `slot_offset` of
+ * every rank's buffer, waits for every rank (bounded, flags in peer memory) and adds the ranks'
+ * partials in rank order, plus `bias` once, into `out` [M, N]: the same bits as nqb200_gemm into the
+ * slot followed by nqb200_peer_allreduce, with one launch and one NVLink crossing less.  The slot
+ * must hold world * M * N * 2 bytes (`slot_bytes` = its size); use slots round-robin (at least 3).
+ * Only where nqb200_gemm_allreduce_supported() says 1, else NQB200_ERR_BAD_SHAPE.  Workspace as for
+ * nqb200_gemm.  No counterpart in the reference (single GPU). */
+int nqb200_gemm_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype, int world,
+                                    size_t slot_bytes);
+int nqb200_gemm_allreduce(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                          const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
+                          int64_t group_size, int dtype, void* workspace, size_t workspace_bytes,
+                          void* const* peer_buffers, int rank, int world, size_t slot_offset, size_t slot_bytes,
+                          void* stream);
 int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int world, size_t slot_offset, void* out,
                           const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype, void* stream);
 

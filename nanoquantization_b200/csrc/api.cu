@@ -1,6 +1,7 @@
 // C ABI of the library: argument checks and kernel choice.  No allocation,
 // no exceptions, no global mutable state.
 #include "common.cuh"
+#include "peer_layout.cuh"
 
 using namespace nqb200;
 
@@ -107,6 +108,39 @@ extern "C" int nqb200_gemm_gate_up_silu(const void* x, const void* qweight, cons
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
   a.epilogue = 1;
+  return launch_stream(a);
+}
+
+extern "C" int nqb200_gemm_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g, int dtype, int world, size_t slot_bytes) {
+  if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0 || world < 2 || world > kMaxRanks) return 0;
+  if ((size_t)world * (size_t)M * (size_t)N * 2 > slot_bytes) return 0;
+  return !umma_prefill_supports(M, N, K, g) && stream_allreduce_supported(M, N, K, g) ? 1 : 0;
+}
+
+extern "C" int nqb200_gemm_allreduce(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                                     const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K, int64_t g,
+                                     int dtype, void* workspace, size_t workspace_bytes, void* const* peer_buffers, int rank,
+                                     int world, size_t slot_offset, size_t slot_bytes, void* stream) {
+  const int st = check_shape(M, N, K, g, dtype);
+  if (st != NQB200_OK) return st;
+  if (M == 0) return NQB200_OK;
+  if (rank < 0 || rank >= world || slot_offset % 16 != 0) return NQB200_ERR_BAD_SHAPE;
+  if (!nqb200_gemm_allreduce_supported(M, N, K, g, dtype, world, slot_bytes)) return NQB200_ERR_BAD_SHAPE;
+  if (!x || !qweight || !qscales || !qzeros || !out || !peer_buffers) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(qscales) || !aligned16(qzeros) || !aligned16(out) ||
+      (bias && !aligned16(bias)))
+    return NQB200_ERR_MISALIGNED;
+  if (bias && bias_dtype != NQB200_F16 && bias_dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  PeerEpilogue pe;
+  for (int r = 0; r < kMaxRanks; ++r) pe.peers[r] = r < world ? (uint8_t*)peer_buffers[r] : nullptr;
+  for (int r = 0; r < world; ++r) if (!pe.peers[r]) return NQB200_ERR_NULL_POINTER;
+  pe.rank = rank; pe.world = world; pe.slot_off = slot_offset;
+  GemmArgs a;
+  a.x = x; a.qw = (const uint32_t*)qweight; a.sc = qscales; a.qz = (const uint32_t*)qzeros;
+  a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
+  a.peer = &pe;
   return launch_stream(a);
 }
 

@@ -49,6 +49,8 @@ struct DecodePlan {
 };
 DecodePlan plan_decode(int64_t M, int64_t N, int64_t K, int64_t g);
 
+struct PeerEpilogue;
+
 struct GemmArgs {
   const void* x; const uint32_t* qw; const void* sc; const uint32_t* qz;
   const void* bias; int bias_dtype; void* out;
@@ -56,6 +58,7 @@ struct GemmArgs {
   int dtype;
   void* ws; size_t ws_bytes;
   cudaStream_t stream;
+  const PeerEpilogue* peer = nullptr;  // all-reduce over peer memory in the reducing kernel (streaming decode kernel only)
   int epilogue = 0;  // 1: the matrix is gate|up, out[M, N/2] = silu(gate) * up (streaming decode kernel only)
 };
 
@@ -70,6 +73,7 @@ bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int stream_launches(int64_t M, int64_t N, int64_t K);
 bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g);
+bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 int umma_prefill_launches(int64_t M, int64_t N, int64_t K);
 bool decode_mma_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 

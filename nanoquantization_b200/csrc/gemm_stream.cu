@@ -35,6 +35,7 @@
 // the workspace status word and drains instead of spinning.
 #include "common.cuh"
 #include "tma_utils.cuh"
+#include "peer_layout.cuh"
 #include <mutex>
 
 namespace nqb200 {
@@ -449,6 +450,85 @@ __global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel
   *reinterpret_cast<uint2*>(p.out + (size_t)m * (SILU ? half_n : p.N) + n) = make_uint2(o0, o1);
 }
 
+// The reducing kernel of a row-parallel linear under tensor parallelism, with the all-reduce over
+// the ranks in the same launch.  Each CTA adds the split-K partial sums of its tile and token as
+// above, rounds them to the 16-bit type (what the GEMM alone would output) and stores them straight
+// into the slot of every rank's peer-mapped buffer (area `source rank` of the slot), then raises its
+// flag on every rank, waits for every rank's flag on its own, adds the ranks' areas of its own slot
+// in rank order (identical bits on all ranks), adds the bias once and writes the output.  One NVLink
+// crossing per value and no launch of its own for the collective.  Flags only grow: each flag set
+// (one per CTA of the grid) counts its own calls in device memory, so the launch can be replayed
+// from a CUDA graph; slots are used round-robin by the caller, so an area is rewritten only after
+// every rank has passed the flags of a later call.  Waits are bounded (about a second) and record
+// NQB200_ERR_WAIT_TIMEOUT in the buffer's status word.  Plain peer stores and loads only.
+template <bool BF16, int kReduceWays>
+__global__ void __launch_bounds__(kUnitN / 4 * kReduceWays)
+stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot_floats, const PeerEpilogue pe) {
+  __shared__ float4 part[kReduceWays][kUnitN / 4];
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int tile = (int)blockIdx.x, m = (int)blockIdx.y;
+  const int t = (int)threadIdx.x, j = (int)threadIdx.y;
+  const int col = 4 * t, n = tile * kUnitN + col;
+  float4 v;
+  reduce_tile_partials<kReduceWays>(p, C, slot_floats, tile, m, col, j, v);
+  part[j][t] = v;
+  const int set = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  uint8_t* mine = pe.peers[pe.rank];
+  if (t == 0 && j == 0) {
+    uint32_t* ep = reinterpret_cast<uint32_t*>(mine + kArOffEpoch2) + set;
+    s_epoch = *ep + 1;
+    *ep = s_epoch;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const bool owner = j == 0 && n < p.N;
+  const size_t mn = (size_t)p.M * p.N, elem = (size_t)m * p.N + n;
+  if (owner) {
+#pragma unroll
+    for (int k = 1; k < kReduceWays; ++k) { const float4 o = part[k][t]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+    const uint2 w = make_uint2((uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16),
+                               (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16));
+    for (int r = 0; r < pe.world; ++r)
+      *reinterpret_cast<uint2*>(pe.peers[r] + kArOffData + pe.slot_off + ((size_t)pe.rank * mn + elem) * 2) = w;
+  }
+  __syncthreads();  // every store of this CTA is ordered before the flags raised below
+  const uint32_t e = s_epoch;
+  const int lin = j * (int)blockDim.x + t;
+  if (lin < pe.world) {
+    st_flag(reinterpret_cast<uint32_t*>(pe.peers[lin] + kArOffFlags2) + (size_t)set * kMaxRanks + pe.rank, e);
+    const uint32_t* ours = reinterpret_cast<const uint32_t*>(mine + kArOffFlags2) + (size_t)set * kMaxRanks + lin;
+    const unsigned long long t0 = global_timer_ns();
+    uint32_t it = 0;
+    while ((int32_t)(ld_flag(ours) - e) < 0) {  // a rank already one call ahead shows e + 1
+      if ((++it & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) {
+        atomicExch(reinterpret_cast<int*>(mine), NQB200_ERR_WAIT_TIMEOUT);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok || !owner) return;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int r = 0; r < pe.world; ++r) {
+    uint32_t w0, w1;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1)
+                 : "l"(mine + kArOffData + pe.slot_off + ((size_t)r * mn + elem) * 2) : "memory");
+    acc[0] += raw16_to_float<BF16>((uint16_t)(w0 & 0xFFFF)); acc[1] += raw16_to_float<BF16>((uint16_t)(w0 >> 16));
+    acc[2] += raw16_to_float<BF16>((uint16_t)(w1 & 0xFFFF)); acc[3] += raw16_to_float<BF16>((uint16_t)(w1 >> 16));
+  }
+  if (p.bias) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] += bias_to_float(p.bias, p.bias_dtype, n + k);
+  }
+  *reinterpret_cast<uint2*>(p.out + elem) =
+      make_uint2((uint32_t)float_to_raw16<BF16>(acc[0]) | ((uint32_t)float_to_raw16<BF16>(acc[1]) << 16),
+                 (uint32_t)float_to_raw16<BF16>(acc[2]) | ((uint32_t)float_to_raw16<BF16>(acc[3]) << 16));
+}
+
 // CTAs of this kernel that one SM holds at a time (0 on error): the persistent grid is sized so
 // that all of it is resident at once.
 template <int MT, bool BF16>
@@ -470,11 +550,15 @@ static int stream_ctas_per_sm() {
 
 template <int MT, bool BF16>
 static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const StreamParams& sp,
-                           int max_contributors, bool silu, cudaStream_t st) {
+                           int max_contributors, bool silu, const PeerEpilogue* peer, cudaStream_t st) {
   // the attributes were set when the occupancy was measured
   const int rc = launch_overlapped(stream_kernel<MT, BF16>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
   if (rc != NQB200_OK || max_contributors <= 1) return rc;
   const int sf = (int)StreamCfg<MT>::kSlotFloats;
+  if (peer)
+    return max_contributors <= 8
+               ? launch_overlapped(stream_reduce_allreduce_kernel<BF16, 1>, dim3(sp.ntiles, sp.M), dim3(kUnitN / 4, 1), 0, st, sp, sp.nctas, sf, *peer)
+               : launch_overlapped(stream_reduce_allreduce_kernel<BF16, 4>, dim3(sp.ntiles, sp.M), dim3(kUnitN / 4, 4), 0, st, sp, sp.nctas, sf, *peer);
   const dim3 grid(silu ? sp.ntiles / 2 : sp.ntiles, sp.M);
   if (max_contributors <= 8)
     return silu ? launch_overlapped(stream_reduce_kernel<BF16, 1, true>, grid, dim3(kUnitN / 4, 1), 0, st, sp, sp.nctas, sf)
@@ -507,6 +591,16 @@ bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
   int fewest = 0;
   stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap), &fewest);
   return fewest >= 2;
+}
+
+// The all-reduce epilogue needs every tile reduced by the second kernel and a flag set per CTA of it.
+bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
+  if (!stream_supports(M, N, K, g)) return false;
+  const int G = (int)(K / 128), ntiles = (int)((N + kUnitN - 1) / kUnitN);
+  const long long U = (long long)ntiles * G, cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
+  int fewest = 0;
+  stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap), &fewest);
+  return fewest >= 2 && (long long)ntiles * M <= kEpilogueSets;
 }
 
 // 2 when some tile needs the reducing kernel.  Assumes the full occupancy the kernel is built for.
@@ -544,8 +638,10 @@ int launch_stream(const GemmArgs& a) {
   const int reduce = stream_max_contributors(ntiles, G, C, &fewest);
   const bool silu = a.epilogue == 1;
   if (silu && (a.N % (2 * kUnitN) != 0 || fewest < 2)) return NQB200_ERR_BAD_SHAPE;
-  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, silu, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, silu, a.stream);
-  return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, silu, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, silu, a.stream);
+  const PeerEpilogue* peer = a.peer;
+  if (peer && (silu || fewest < 2 || (long long)ntiles * a.M > kEpilogueSets)) return NQB200_ERR_BAD_SHAPE;
+  if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, silu, peer, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, silu, peer, a.stream);
+  return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, silu, peer, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, silu, peer, a.stream);
 }
 
 }  // namespace nqb200

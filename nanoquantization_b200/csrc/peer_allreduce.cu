@@ -18,15 +18,11 @@
 // Only plain peer loads and stores are used: no multimem, no TMA.
 #include "common.cuh"
 #include "tma_utils.cuh"
+#include "peer_layout.cuh"
 
 namespace nqb200 {
 
-constexpr int kMaxRanks = 8;
-constexpr int kArBlocks = 32;            // CTAs per call; each has its own flag set
 constexpr int kArThreads = 256;
-// layout of a rank's comm buffer: [status 256 B][epochs kArBlocks x u32, padded to 256 B]
-//                                  [flags kArBlocks x kMaxRanks x u32][data slots]
-constexpr size_t kArOffEpoch = 256, kArOffFlags = 512, kArOffData = 4096;
 
 struct ArParams {
   uint8_t* peers[kMaxRanks];   // every rank's comm buffer as mapped into this process (peers[rank] is our own)
@@ -39,12 +35,6 @@ struct ArParams {
   int N;                       // row length, for the bias
 };
 
-__device__ __forceinline__ void st_flag(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_flag(const uint32_t* p) {
-  uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
-}
 __device__ __forceinline__ uint4 ld_peer(const uint4* p) {
   uint4 v; asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;

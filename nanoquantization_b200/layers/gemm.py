@@ -82,12 +82,14 @@ _ws_bytes_cache: dict[tuple, int] = {}
 
 
 def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros: torch.Tensor,
-           bias: torch.Tensor | None, out: torch.Tensor | None = None, silu_mul: bool = False) -> torch.Tensor:
+           bias: torch.Tensor | None, out: torch.Tensor | None = None, silu_mul: bool = False, peer=None) -> torch.Tensor:
     """One fused call: out = x @ ((q - z) * s) (+ bias), any M.  ``out`` may name a preallocated
     contiguous ``[M, N]`` tensor of the output dtype (e.g. a slot of a peer-mapped buffer).
     ``silu_mul``: the matrix is a merged gate|up projection and the result is
     ``silu(y[:, :N/2]) * y[:, N/2:]`` (``[M, N/2]``); the caller has checked that the library
-    supports it for this shape."""
+    supports it for this shape.  ``peer = (buffers, rank, world, slot_offset, slot_bytes)``: the
+    linear is a row-parallel shard and the result is the sum over the ranks, reduced over peer
+    memory by the kernel that finishes the GEMM (again only where the library supports it)."""
     M, K = x.shape
     N = qweight.shape[1] * 8
     group_size = K // qscales.shape[0]
@@ -111,6 +113,10 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
         return out
     lib = _lib.load()
     entry = lib.nqb200_gemm_gate_up_silu if silu_mul else lib.nqb200_gemm
+    tail = (_lib.stream_ptr(),)
+    if peer is not None:
+        assert not silu_mul
+        entry, tail = lib.nqb200_gemm_allreduce, tuple(peer) + tail
     key = (M, N, K, group_size, code)
     nbytes = _ws_bytes_cache.get(key)
     if nbytes is None:
@@ -123,8 +129,7 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
         ws = _lib.workspace(dev, nbytes)
         status = entry(x.data_ptr(), qweight.data_ptr(), qscales.data_ptr(), qzeros.data_ptr(),
                        bias_ptr, bias_code, out.data_ptr(), M, N, K, group_size, code,
-                       ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-                       _lib.stream_ptr())
+                       ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, *tail)
     finally:
         if other_device:
             torch.cuda.set_device(prev)

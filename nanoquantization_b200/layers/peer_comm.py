@@ -4,7 +4,9 @@
 row-parallel linear writes its partial ``[M, N]`` result straight into a slot of that buffer
 (``WQLinear_GEMM.forward(x, out=slot)``) and ``reduce`` launches one kernel per rank that waits
 for all ranks, adds the peers' slots in rank order and writes the sum to an ordinary tensor.
-Messages larger than a slot go through NCCL.  The reference has no counterpart.
+For decode-sized inputs ``linear_all_reduce`` does both in the GEMM itself: the kernel that adds the
+GEMM's split-K partial sums stores the rank's result into every peer's slot and reduces over the
+ranks (``nqb200_gemm_allreduce``).  Messages larger than a slot go through NCCL.  The reference has no counterpart.
 """
 from __future__ import annotations
 
@@ -24,8 +26,9 @@ class _DevicePtr:
 
 
 class PeerAllReduce:
-    def __init__(self, group=None, slot_bytes: int = 1 << 20, num_slots: int = 8):
+    def __init__(self, group=None, slot_bytes: int = 1 << 20, num_slots: int = 8, fused: bool = True):
         assert num_slots >= 3
+        self.fused = fused  # reduce inside the GEMM's finishing kernel where the library supports it
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.slot_bytes, self.num_slots, self._next = slot_bytes, num_slots, 0
@@ -78,6 +81,15 @@ class PeerAllReduce:
             y = linear(x)
             dist.all_reduce(y, group=self.group)
             return y
+        dtype = linear.qscales.dtype
+        if self.fused and _lib.load().nqb200_gemm_allreduce_supported(M, N, x.shape[1], linear.group_size, _lib.dtype_code(dtype),
+                                                                      self.world, self.slot_bytes):
+            # the kernel that finishes the GEMM also reduces over the ranks
+            from .gemm import _w4a16
+            off = self._next * self.slot_bytes
+            self._next = (self._next + 1) % self.num_slots
+            return _w4a16(x, linear.qweight, linear.qscales, linear.qzeros, linear.bias, None,
+                          peer=(self._ptrs, self.rank, self.world, off, self.slot_bytes))
         slot, off = self.next_slot(M, N, linear.qscales.dtype)
         linear(x, out=slot)
         return self.reduce(off, M, N, linear.qscales.dtype)

@@ -54,6 +54,13 @@ def _worker(rank, world, port, out):
         errs.append(0.0 if same else 1.0)
         errs.append(float((outs[0].float() - ref_nccl.float()).abs().max() / full.abs().max()))
         errs.append(float(comm.status()))
+        # the reduction inside the GEMM's finishing kernel (the default above) and the stand-alone
+        # all-reduce kernel after a GEMM into the slot give the same bits
+        plain = PeerAllReduce(slot_bytes=1 << 18, num_slots=4, fused=False)
+        outs2 = [plain.linear_all_reduce(row.shard, xs) for _ in range(5)]
+        errs.append(0.0 if all(torch.equal(o, outs[0]) for o in outs2) else 1.0)
+        errs.append(float(plain.status()))
+        plain.close()
         big = comm.linear_all_reduce(row.shard, torch.randn(600, 512, device=dev, dtype=torch.float16))  # too large: NCCL path
         assert big.shape == (600, 512)
         comm.close()
