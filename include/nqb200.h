@@ -93,6 +93,37 @@ int nqb200_gemm_gate_up_silu(const void* x, const void* qweight, const void* qsc
                              const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
                              int64_t group_size, int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The decode-sized linear with what surrounds it in a Qwen3 block, in its own two launches (the
+ * streaming kernel and the kernel that adds its split-K partial sums).  Any combination that
+ * nqb200_gemm_decode_fused_supported() accepts (flags = OR of NQB200_FUSE_*):
+ *   RMSNORM   x is the residual stream h [M, K]; the linear's input is RMSNorm(h) * norm_weight
+ *             (layers/norm.py:18-32 of the reference, same roundings), with mean(h^2) taken from sums
+ *             of squares per token and 512-column tile of h: norm_ssq [M, norm_tiles], fp32.
+ *   RESIDUAL  out [M, N] = 16-bit(16-bit(y) + residual_in) (models/qwen3_quantized.py:213-214), the
+ *             new residual stream, and ssq_out [M, ceil(N/512)] = its sums of squares per token and
+ *             tile: what the RMSNORM prologue of the next linear reads.
+ *   SILU_MUL  as nqb200_gemm_gate_up_silu (out is [M, N/2]); not together with RESIDUAL or ALLREDUCE.
+ *   ALLREDUCE as nqb200_gemm_allreduce (peer_buffers != NULL); the residual is added after the sum.
+ * A block then costs two launches per linear and nothing for its norms, activation and all-reduces.
+ * No counterpart in the reference (its block is separate modules). */
+enum { NQB200_FUSE_RMSNORM = 1, NQB200_FUSE_RESIDUAL = 2, NQB200_FUSE_SILU_MUL = 4, NQB200_FUSE_ALLREDUCE = 8 };
+typedef struct nqb200_decode_fusion {
+  const float* norm_ssq;   /* NULL: x is used as it is */
+  int64_t norm_tiles;
+  const void* norm_weight; /* [K], the model dtype */
+  float norm_eps;
+  int silu_mul;
+  const void* residual_in; /* NULL: out = y */
+  float* ssq_out;
+} nqb200_decode_fusion;
+int nqb200_gemm_decode_fused_supported(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype, int flags,
+                                       int world, size_t slot_bytes);
+int nqb200_gemm_decode_fused(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                             const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K,
+                             int64_t group_size, int dtype, void* workspace, size_t workspace_bytes,
+                             const nqb200_decode_fusion* fusion, void* const* peer_buffers, int rank, int world,
+                             size_t slot_offset, size_t slot_bytes, void* stream);
+
 /* nqb200_gemm for up to 16 tokens without any device allocation by anyone.
  * It has no counterpart in the reference.  It is for callers that cannot
  * provide a scratch buffer because they cannot allocate: hosts that own all

@@ -17,6 +17,15 @@ LIB_PATH = os.path.join(_HERE, "lib", "libnqb200.so")
 F16, BF16 = 0, 1
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
 
+class DecodeFusion(ctypes.Structure):
+    """nqb200_decode_fusion of include/nqb200.h."""
+    _fields_ = [("norm_ssq", ctypes.c_void_p), ("norm_tiles", ctypes.c_int64), ("norm_weight", ctypes.c_void_p),
+                ("norm_eps", ctypes.c_float), ("silu_mul", ctypes.c_int), ("residual_in", ctypes.c_void_p),
+                ("ssq_out", ctypes.c_void_p)]
+
+
+FUSE_RMSNORM, FUSE_RESIDUAL, FUSE_SILU_MUL, FUSE_ALLREDUCE = 1, 2, 4, 8
+
 # name -> (restype, argtypes); mirrors include/nqb200.h one to one
 SIGNATURES = {
     "nqb200_version": (_int, []),
@@ -28,6 +37,9 @@ SIGNATURES = {
     "nqb200_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "nqb200_gemm_gate_up_silu_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
     "nqb200_gemm_gate_up_silu": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "nqb200_gemm_decode_fused_supported": (_int, [_i64, _i64, _i64, _i64, _int, _int, _int, _sz]),
+    "nqb200_gemm_decode_fused": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz,
+                                 ctypes.POINTER(DecodeFusion), ctypes.POINTER(_vp), _int, _int, _sz, _sz, _vp]),
     "nqb200_gemm_decode_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
     "nqb200_quantize_pack": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nqb200_add_rmsnorm": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, _int, _vp]),

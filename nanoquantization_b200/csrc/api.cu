@@ -144,6 +144,56 @@ extern "C" int nqb200_gemm_allreduce(const void* x, const void* qweight, const v
   return launch_stream(a);
 }
 
+extern "C" int nqb200_gemm_decode_fused_supported(int64_t M, int64_t N, int64_t K, int64_t g, int dtype, int flags, int world,
+                                                  size_t slot_bytes) {
+  if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0 || umma_prefill_supports(M, N, K, g)) return 0;
+  if (!stream_supports(M, N, K, g)) return 0;
+  const bool silu = flags & NQB200_FUSE_SILU_MUL, residual = flags & NQB200_FUSE_RESIDUAL, ar = flags & NQB200_FUSE_ALLREDUCE;
+  if (silu && (residual || ar)) return 0;
+  if (silu && !stream_silu_supported(M, N, K, g)) return 0;
+  if ((residual || ar) && !stream_allreduce_supported(M, N, K, g)) return 0;  // every tile finished by the reducing kernel
+  if (ar && (world < 2 || world > kMaxRanks || (size_t)world * (size_t)M * (size_t)N * 2 > slot_bytes)) return 0;
+  return 1;
+}
+
+extern "C" int nqb200_gemm_decode_fused(const void* x, const void* qweight, const void* qscales, const void* qzeros,
+                                        const void* bias, int bias_dtype, void* out, int64_t M, int64_t N, int64_t K, int64_t g,
+                                        int dtype, void* workspace, size_t workspace_bytes, const nqb200_decode_fusion* f,
+                                        void* const* peer_buffers, int rank, int world, size_t slot_offset, size_t slot_bytes,
+                                        void* stream) {
+  const int st = check_shape(M, N, K, g, dtype);
+  if (st != NQB200_OK) return st;
+  if (M == 0) return NQB200_OK;
+  if (!f) return NQB200_ERR_NULL_POINTER;
+  const int flags = (f->norm_ssq ? NQB200_FUSE_RMSNORM : 0) | (f->residual_in ? NQB200_FUSE_RESIDUAL : 0) |
+                    (f->silu_mul ? NQB200_FUSE_SILU_MUL : 0) | (peer_buffers ? NQB200_FUSE_ALLREDUCE : 0);
+  if (!nqb200_gemm_decode_fused_supported(M, N, K, g, dtype, flags, world, slot_bytes)) return NQB200_ERR_BAD_SHAPE;
+  if (!x || !qweight || !qscales || !qzeros || !out) return NQB200_ERR_NULL_POINTER;
+  if (f->norm_ssq && (!f->norm_weight || f->norm_tiles <= 0)) return NQB200_ERR_NULL_POINTER;
+  if (f->residual_in && !f->ssq_out) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(qscales) || !aligned16(qzeros) || !aligned16(out) ||
+      (bias && !aligned16(bias)) || (f->residual_in && !aligned16(f->residual_in)) || (f->norm_weight && !aligned16(f->norm_weight)))
+    return NQB200_ERR_MISALIGNED;
+  if (bias && bias_dtype != NQB200_F16 && bias_dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  PeerEpilogue pe;
+  if (peer_buffers) {
+    if (rank < 0 || rank >= world || slot_offset % 16 != 0) return NQB200_ERR_BAD_SHAPE;
+    for (int r = 0; r < kMaxRanks; ++r) pe.peers[r] = r < world ? (uint8_t*)peer_buffers[r] : nullptr;
+    for (int r = 0; r < world; ++r) if (!pe.peers[r]) return NQB200_ERR_NULL_POINTER;
+    pe.rank = rank; pe.world = world; pe.slot_off = slot_offset;
+  }
+  GemmArgs a;
+  a.x = x; a.qw = (const uint32_t*)qweight; a.sc = qscales; a.qz = (const uint32_t*)qzeros;
+  a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
+  a.norm_ssq = f->norm_ssq; a.norm_tiles = (int)f->norm_tiles; a.norm_weight = f->norm_weight; a.norm_eps = f->norm_eps;
+  a.residual_in = f->residual_in; a.ssq_out = f->ssq_out;
+  a.epilogue = f->silu_mul ? 1 : 0;
+  a.peer = peer_buffers ? &pe : nullptr;
+  return launch_stream(a);
+}
+
 extern "C" int nqb200_workspace_status(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace) return NQB200_ERR_NULL_POINTER;
   if (workspace_bytes < (size_t)kCounterBytes) return NQB200_ERR_WORKSPACE;

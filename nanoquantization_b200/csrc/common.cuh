@@ -58,6 +58,10 @@ struct GemmArgs {
   int dtype;
   void* ws; size_t ws_bytes;
   cudaStream_t stream;
+  // streaming decode kernel only: RMSNorm of the input from per-tile sums of squares; residual add and
+  // sums of squares of the output (see StreamParams)
+  const float* norm_ssq = nullptr; int norm_tiles = 0; const void* norm_weight = nullptr; float norm_eps = 0.f;
+  const void* residual_in = nullptr; float* ssq_out = nullptr;
   const PeerEpilogue* peer = nullptr;  // all-reduce over peer memory in the reducing kernel (streaming decode kernel only)
   int epilogue = 0;  // 1: the matrix is gate|up, out[M, N/2] = silu(gate) * up (streaming decode kernel only)
 };

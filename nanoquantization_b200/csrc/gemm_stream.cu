@@ -68,6 +68,12 @@ struct StreamParams {
   int M, N, K, G, ntiles, nctas;
   uint32_t U;
   int* counters; float* slots;
+  // Optional prologue: x is a residual stream h and the GEMM input is RMSNorm(h) * norm_weight, with
+  // mean(h^2) given as sums of squares per (token, 512-column tile of h): norm_ssq[M][norm_tiles].
+  const float* norm_ssq; int norm_tiles; const uint16_t* norm_weight; float norm_eps;
+  // Optional epilogue of the reducing kernel: out = 16-bit(16-bit(y) + residual_in) (the new residual
+  // stream) and its sums of squares per (token, tile) into ssq_out[M][ntiles].
+  const uint16_t* residual_in; float* ssq_out;
 };
 
 bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
@@ -103,7 +109,7 @@ __device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t U, uint32_t C) {
 // value of column e (0..7) of a thread's 8-column group, row t of the token pair
 #define NQ_TOTAL_AT(tot, e, t) tot[((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) >> 1][2 * (((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) & 1) + (t)]
 
-template <int MT, bool BF16>
+template <int MT, bool BF16, bool NORM>
 __global__ void __launch_bounds__(kStreamThreads, StreamCfg<MT>::kCtasPerSm)
 stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
               const __grid_constant__ CUtensorMap tm_z, const StreamParams p) {
@@ -174,6 +180,17 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     // the next token's.
     const int cc = lane & 15, half = lane >> 4;
     int grp = (int)(u_begin % G);
+    // With the RMSNorm prologue: 1 / rms of token `lane` from the per-tile sums of squares (added
+    // in tile order), handed to the lanes that need it by shuffles.
+    float inv_mine = 0.f;
+    if (NORM && lane < p.M) {
+      float tot = 0.f;
+      for (int tl = 0; tl < p.norm_tiles; ++tl) tot += __ldcg(p.norm_ssq + (size_t)lane * p.norm_tiles + tl);
+      inv_mine = rsqrtf(tot / (float)p.K + p.norm_eps);
+    }
+    float inv_tok[4 * MT];
+#pragma unroll
+    for (int j = 0; j < 4 * MT; ++j) inv_tok[j] = __shfl_sync(0xFFFFFFFFu, inv_mine, (2 * j + half) & 31);
     for (int i = 0; i < nunits; ++i) {
       const int s = i % kStages;
       if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) {
@@ -187,9 +204,24 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         const int m = 2 * j + half;
         v[j] = m < p.M ? __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + grp * kUnitK) + cc) : make_uint4(0u, 0u, 0u, 0u);
       }
+      uint4 nw = make_uint4(0u, 0u, 0u, 0u);
+      if (NORM) nw = __ldg(reinterpret_cast<const uint4*>(p.norm_weight + grp * kUnitK) + cc);
 #pragma unroll
       for (int j = 0; j < 4 * MT; ++j) {
         const int m = 2 * j + half;
+        if (NORM) {
+          // 16-bit(16-bit(h * inv) * w), the roundings of the norm as a kernel of its own
+          const uint32_t hw[4] = {v[j].x, v[j].y, v[j].z, v[j].w}, ww[4] = {nw.x, nw.y, nw.z, nw.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a0 = raw16_to_float<BF16>(float_to_raw16<BF16>(raw16_to_float<BF16>((uint16_t)(hw[e] & 0xFFFF)) * inv_tok[j]));
+            const float a1 = raw16_to_float<BF16>(float_to_raw16<BF16>(raw16_to_float<BF16>((uint16_t)(hw[e] >> 16)) * inv_tok[j]));
+            o[e] = (uint32_t)float_to_raw16<BF16>(a0 * raw16_to_float<BF16>((uint16_t)(ww[e] & 0xFFFF))) |
+                   ((uint32_t)float_to_raw16<BF16>(a1 * raw16_to_float<BF16>((uint16_t)(ww[e] >> 16))) << 16);
+          }
+          v[j] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
         *reinterpret_cast<uint4*>(st + ((cc >> 3) ? kOffX1 : kOffX0) + m * 128 + (((cc & 7) ^ (m & 7)) << 4)) = v[j];
         const uint32_t wds[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
         float a = 0.f;
@@ -394,6 +426,44 @@ __device__ __forceinline__ int reduce_tile_partials(const StreamParams& p, int C
   return nc;
 }
 
+// Last step of the reducing kernels, called by every thread of the CTA: the owner threads (one per
+// four columns) hold the finished fp32 values `a`.  Without a residual they are rounded and stored to
+// out.  With one, out gets the new residual stream 16-bit(16-bit(a) + residual_in) and the CTA adds
+// the squares of what it stored into ssq_out[token][tile] (shuffles, then the four owner warps in
+// order), for the RMSNorm prologue of the next linear.
+template <bool BF16>
+__device__ __forceinline__ void store_reduced(const StreamParams& p, int tile, int m, int n, bool owner, const float (&a)[4],
+                                              float* s_red) {
+  const size_t elem = (size_t)m * p.N + n;
+  if (!p.residual_in) {
+    if (owner)
+      *reinterpret_cast<uint2*>(p.out + elem) =
+          make_uint2((uint32_t)float_to_raw16<BF16>(a[0]) | ((uint32_t)float_to_raw16<BF16>(a[1]) << 16),
+                     (uint32_t)float_to_raw16<BF16>(a[2]) | ((uint32_t)float_to_raw16<BF16>(a[3]) << 16));
+    return;
+  }
+  float ss = 0.f;
+  if (owner) {
+    const uint2 r = __ldcg(reinterpret_cast<const uint2*>(p.residual_in + elem));
+    const uint32_t rw[2] = {r.x, r.y};
+    uint16_t h[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float y = raw16_to_float<BF16>(float_to_raw16<BF16>(a[k]));
+      h[k] = float_to_raw16<BF16>(y + raw16_to_float<BF16>((uint16_t)((rw[k >> 1] >> (16 * (k & 1))) & 0xFFFF)));
+      const float hf = raw16_to_float<BF16>(h[k]);
+      ss += hf * hf;
+    }
+    *reinterpret_cast<uint2*>(p.out + elem) = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+  }
+  const int lin = (int)(threadIdx.y * blockDim.x + threadIdx.x);  // owners are threads 0..127: warps 0..3
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+  if (lin < 128 && (lin & 31) == 0) s_red[lin >> 5] = ss;
+  __syncthreads();
+  if (lin == 0) p.ssq_out[(size_t)m * p.ntiles + tile] = ((s_red[0] + s_red[1]) + s_red[2]) + s_red[3];
+}
+
 // Adds the partial segments of one tile (blockIdx.x) and token (blockIdx.y).  Thread (t, j) owns
 // columns 4t..4t+3 and the contributors j, j+W, j+2W, ... (W = 1 when a tile has at most eight
 // contributors, else 4); the W partial sums of a column meet in shared memory, always in the same
@@ -421,22 +491,25 @@ __global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel
   part[0][j][t] = v;
   if (SILU) part[SILU ? 1 : 0][j][t] = u;
   __syncthreads();
-  if (j != 0 || n >= (SILU ? half_n : p.N)) return;
+  const bool owner = j == 0 && n < (SILU ? half_n : p.N);
+  if (owner) {
 #pragma unroll
-  for (int k = 1; k < kReduceWays; ++k) {
-    const float4 o = part[0][k][t];
-    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-    if (SILU) { const float4 o2 = part[SILU ? 1 : 0][k][t]; u.x += o2.x; u.y += o2.y; u.z += o2.z; u.w += o2.w; }
-  }
-  if (p.bias) {
-    v.x += bias_to_float(p.bias, p.bias_dtype, n); v.y += bias_to_float(p.bias, p.bias_dtype, n + 1);
-    v.z += bias_to_float(p.bias, p.bias_dtype, n + 2); v.w += bias_to_float(p.bias, p.bias_dtype, n + 3);
-    if (SILU) {
-      u.x += bias_to_float(p.bias, p.bias_dtype, half_n + n); u.y += bias_to_float(p.bias, p.bias_dtype, half_n + n + 1);
-      u.z += bias_to_float(p.bias, p.bias_dtype, half_n + n + 2); u.w += bias_to_float(p.bias, p.bias_dtype, half_n + n + 3);
+    for (int k = 1; k < kReduceWays; ++k) {
+      const float4 o = part[0][k][t];
+      v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+      if (SILU) { const float4 o2 = part[SILU ? 1 : 0][k][t]; u.x += o2.x; u.y += o2.y; u.z += o2.z; u.w += o2.w; }
+    }
+    if (p.bias) {
+      v.x += bias_to_float(p.bias, p.bias_dtype, n); v.y += bias_to_float(p.bias, p.bias_dtype, n + 1);
+      v.z += bias_to_float(p.bias, p.bias_dtype, n + 2); v.w += bias_to_float(p.bias, p.bias_dtype, n + 3);
+      if (SILU) {
+        u.x += bias_to_float(p.bias, p.bias_dtype, half_n + n); u.y += bias_to_float(p.bias, p.bias_dtype, half_n + n + 1);
+        u.z += bias_to_float(p.bias, p.bias_dtype, half_n + n + 2); u.w += bias_to_float(p.bias, p.bias_dtype, half_n + n + 3);
+      }
     }
   }
   if (SILU) {
+    if (!owner) return;
     auto act = [](float g, float up) {
       g = raw16_to_float<BF16>(float_to_raw16<BF16>(g));
       up = raw16_to_float<BF16>(float_to_raw16<BF16>(up));
@@ -444,10 +517,14 @@ __global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel
       return sl * up;
     };
     v.x = act(v.x, u.x); v.y = act(v.y, u.y); v.z = act(v.z, u.z); v.w = act(v.w, u.w);
+    const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
+    const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
+    *reinterpret_cast<uint2*>(p.out + (size_t)m * half_n + n) = make_uint2(o0, o1);
+    return;
   }
-  const uint32_t o0 = (uint32_t)float_to_raw16<BF16>(v.x) | ((uint32_t)float_to_raw16<BF16>(v.y) << 16);
-  const uint32_t o1 = (uint32_t)float_to_raw16<BF16>(v.z) | ((uint32_t)float_to_raw16<BF16>(v.w) << 16);
-  *reinterpret_cast<uint2*>(p.out + (size_t)m * (SILU ? half_n : p.N) + n) = make_uint2(o0, o1);
+  __shared__ float s_red[4];
+  const float a[4] = {v.x, v.y, v.z, v.w};
+  store_reduced<BF16>(p, tile, m, n, owner, a, s_red);
 }
 
 // The reducing kernel of a row-parallel linear under tensor parallelism, with the all-reduce over
@@ -463,7 +540,7 @@ __global__ void __launch_bounds__(kUnitN / 4 * kReduceWays) stream_reduce_kernel
 // NQB200_ERR_WAIT_TIMEOUT in the buffer's status word.  Plain peer stores and loads only.
 template <bool BF16, int kReduceWays>
 __global__ void __launch_bounds__(kUnitN / 4 * kReduceWays)
-stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot_floats, const PeerEpilogue pe) {
+stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot_floats, const __grid_constant__ PeerEpilogue pe) {
   __shared__ float4 part[kReduceWays][kUnitN / 4];
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
@@ -511,22 +588,23 @@ stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot
     }
   }
   __syncthreads();
-  if (!s_ok || !owner) return;
+  if (!s_ok) return;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int r = 0; r < pe.world; ++r) {
-    uint32_t w0, w1;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1)
-                 : "l"(mine + kArOffData + pe.slot_off + ((size_t)r * mn + elem) * 2) : "memory");
-    acc[0] += raw16_to_float<BF16>((uint16_t)(w0 & 0xFFFF)); acc[1] += raw16_to_float<BF16>((uint16_t)(w0 >> 16));
-    acc[2] += raw16_to_float<BF16>((uint16_t)(w1 & 0xFFFF)); acc[3] += raw16_to_float<BF16>((uint16_t)(w1 >> 16));
-  }
-  if (p.bias) {
+  if (owner) {
+    for (int r = 0; r < pe.world; ++r) {
+      uint32_t w0, w1;
+      asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1)
+                   : "l"(mine + kArOffData + pe.slot_off + ((size_t)r * mn + elem) * 2) : "memory");
+      acc[0] += raw16_to_float<BF16>((uint16_t)(w0 & 0xFFFF)); acc[1] += raw16_to_float<BF16>((uint16_t)(w0 >> 16));
+      acc[2] += raw16_to_float<BF16>((uint16_t)(w1 & 0xFFFF)); acc[3] += raw16_to_float<BF16>((uint16_t)(w1 >> 16));
+    }
+    if (p.bias) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) acc[k] += bias_to_float(p.bias, p.bias_dtype, n + k);
+      for (int k = 0; k < 4; ++k) acc[k] += bias_to_float(p.bias, p.bias_dtype, n + k);
+    }
   }
-  *reinterpret_cast<uint2*>(p.out + elem) =
-      make_uint2((uint32_t)float_to_raw16<BF16>(acc[0]) | ((uint32_t)float_to_raw16<BF16>(acc[1]) << 16),
-                 (uint32_t)float_to_raw16<BF16>(acc[2]) | ((uint32_t)float_to_raw16<BF16>(acc[3]) << 16));
+  __shared__ float s_red[4];
+  store_reduced<BF16>(p, tile, m, n, owner, acc, s_red);
 }
 
 // CTAs of this kernel that one SM holds at a time (0 on error): the persistent grid is sized so
@@ -537,12 +615,17 @@ static int stream_ctas_per_sm() {
   if (occ < 0) {
     constexpr int kStreamSmem = StreamCfg<MT>::kSmem;
     int n = 0;
-    if (cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(stream_kernel<MT, BF16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_kernel<MT, BF16>, kStreamThreads, kStreamSmem) != cudaSuccess) {
+    int n2 = 0;
+    if (cudaFuncSetAttribute(stream_kernel<MT, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_kernel<MT, BF16, false>, kStreamThreads, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n2, stream_kernel<MT, BF16, true>, kStreamThreads, kStreamSmem) != cudaSuccess) {
       cudaGetLastError();
       return 0;
     }
+    if (n2 < n) n = n2;
     occ = n < StreamCfg<MT>::kCtasPerSm ? n : StreamCfg<MT>::kCtasPerSm;
   }
   return occ;
@@ -552,7 +635,8 @@ template <int MT, bool BF16>
 static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const StreamParams& sp,
                            int max_contributors, bool silu, const PeerEpilogue* peer, cudaStream_t st) {
   // the attributes were set when the occupancy was measured
-  const int rc = launch_overlapped(stream_kernel<MT, BF16>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
+  const int rc = sp.norm_ssq ? launch_overlapped(stream_kernel<MT, BF16, true>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp)
+                             : launch_overlapped(stream_kernel<MT, BF16, false>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
   if (rc != NQB200_OK || max_contributors <= 1) return rc;
   const int sf = (int)StreamCfg<MT>::kSlotFloats;
   if (peer)
@@ -634,12 +718,16 @@ int launch_stream(const GemmArgs& a) {
   sp.x = (const uint16_t*)a.x;
   sp.M = a.M; sp.N = a.N; sp.K = a.K; sp.G = G; sp.ntiles = ntiles; sp.nctas = C; sp.U = (uint32_t)U;
   sp.counters = (int*)a.ws; sp.slots = (float*)((char*)a.ws + kCounterBytes);
+  sp.norm_ssq = a.norm_ssq; sp.norm_tiles = a.norm_tiles; sp.norm_weight = (const uint16_t*)a.norm_weight; sp.norm_eps = a.norm_eps;
+  sp.residual_in = (const uint16_t*)a.residual_in; sp.ssq_out = a.ssq_out;
   int fewest = 0;
   const int reduce = stream_max_contributors(ntiles, G, C, &fewest);
   const bool silu = a.epilogue == 1;
   if (silu && (a.N % (2 * kUnitN) != 0 || fewest < 2)) return NQB200_ERR_BAD_SHAPE;
   const PeerEpilogue* peer = a.peer;
   if (peer && (silu || fewest < 2 || (long long)ntiles * a.M > kEpilogueSets)) return NQB200_ERR_BAD_SHAPE;
+  if (a.residual_in && (silu || fewest < 2 || !a.ssq_out)) return NQB200_ERR_BAD_SHAPE;
+  if (a.norm_ssq && (!a.norm_weight || a.norm_tiles <= 0)) return NQB200_ERR_BAD_SHAPE;
   if (mt == 1) return bf ? launch_stream_t<1, true>(tw, ts, tz, sp, reduce, silu, peer, a.stream) : launch_stream_t<1, false>(tw, ts, tz, sp, reduce, silu, peer, a.stream);
   return bf ? launch_stream_t<2, true>(tw, ts, tz, sp, reduce, silu, peer, a.stream) : launch_stream_t<2, false>(tw, ts, tz, sp, reduce, silu, peer, a.stream);
 }

@@ -14,6 +14,8 @@ library is missing or the tensors are not on a B200.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 import torch.nn as nn
 
@@ -82,14 +84,18 @@ _ws_bytes_cache: dict[tuple, int] = {}
 
 
 def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros: torch.Tensor,
-           bias: torch.Tensor | None, out: torch.Tensor | None = None, silu_mul: bool = False, peer=None) -> torch.Tensor:
+           bias: torch.Tensor | None, out: torch.Tensor | None = None, silu_mul: bool = False, peer=None,
+           norm=None, residual: torch.Tensor | None = None):
     """One fused call: out = x @ ((q - z) * s) (+ bias), any M.  ``out`` may name a preallocated
     contiguous ``[M, N]`` tensor of the output dtype (e.g. a slot of a peer-mapped buffer).
     ``silu_mul``: the matrix is a merged gate|up projection and the result is
     ``silu(y[:, :N/2]) * y[:, N/2:]`` (``[M, N/2]``); the caller has checked that the library
     supports it for this shape.  ``peer = (buffers, rank, world, slot_offset, slot_bytes)``: the
     linear is a row-parallel shard and the result is the sum over the ranks, reduced over peer
-    memory by the kernel that finishes the GEMM (again only where the library supports it)."""
+    memory by the kernel that finishes the GEMM (again only where the library supports it).
+    ``norm = (ssq, weight, eps)``: ``x`` is a residual stream and the input is its RMSNorm, computed
+    on the fly from per-tile sums of squares ``ssq [M, tiles]``.  ``residual``: the result is
+    ``(16-bit(y) + residual, ssq_out)``, the new residual stream and its per-tile sums of squares."""
     M, K = x.shape
     N = qweight.shape[1] * 8
     group_size = K // qscales.shape[0]
@@ -114,7 +120,21 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
     lib = _lib.load()
     entry = lib.nqb200_gemm_gate_up_silu if silu_mul else lib.nqb200_gemm
     tail = (_lib.stream_ptr(),)
-    if peer is not None:
+    ssq_out = None
+    if norm is not None or residual is not None:
+        f = _lib.DecodeFusion()
+        f.silu_mul = int(silu_mul)
+        if norm is not None:
+            ssq, nweight, eps = norm
+            assert ssq.dtype == torch.float32 and ssq.is_contiguous() and ssq.shape[0] == M and nweight.dtype == dtype
+            f.norm_ssq, f.norm_tiles, f.norm_weight, f.norm_eps = ssq.data_ptr(), ssq.shape[1], nweight.data_ptr(), float(eps)
+        if residual is not None:
+            assert residual.shape == (M, N) and residual.dtype == dtype and residual.is_contiguous()
+            ssq_out = torch.empty(M, (N + 511) // 512, dtype=torch.float32, device=dev)
+            f.residual_in, f.ssq_out = residual.data_ptr(), ssq_out.data_ptr()
+        entry = lib.nqb200_gemm_decode_fused
+        tail = (ctypes.byref(f),) + (tuple(peer) if peer is not None else (None, 0, 0, 0, 0)) + tail
+    elif peer is not None:
         assert not silu_mul
         entry, tail = lib.nqb200_gemm_allreduce, tuple(peer) + tail
     key = (M, N, K, group_size, code)
@@ -135,7 +155,7 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
             torch.cuda.set_device(prev)
     if status:
         _lib.check(status)
-    return out
+    return (out, ssq_out) if ssq_out is not None else out
 
 
 def awq_gemm(
@@ -302,6 +322,24 @@ class WQLinear_GEMM(nn.Module):
         else:
             out = fused.silu_mul(_w4a16(x2, self.qweight, self.qscales, self.qzeros, self.bias, None))
         return out.reshape(x.shape[:-1] + (self.out_features // 2,))
+
+    def fused_supported(self, M: int, *, norm: bool = False, residual: bool = False, silu_mul: bool = False,
+                        world: int = 0, slot_bytes: int = 0) -> bool:
+        """Whether ``forward_fused`` takes ``M`` tokens with this combination (decode sizes only)."""
+        flags = (_lib.FUSE_RMSNORM if norm else 0) | (_lib.FUSE_RESIDUAL if residual else 0) | \
+                (_lib.FUSE_SILU_MUL if silu_mul else 0) | (_lib.FUSE_ALLREDUCE if world > 1 else 0)
+        return bool(_lib.load().nqb200_gemm_decode_fused_supported(M, self.out_features, self.in_features, self.group_size,
+                                                                   _lib.dtype_code(self.qscales.dtype), flags, world, slot_bytes))
+
+    @torch.no_grad()
+    def forward_fused(self, x: torch.Tensor, *, norm=None, residual: torch.Tensor | None = None, silu_mul: bool = False,
+                      peer=None):
+        """The linear with its neighbours in a Qwen3 block, for ``x [M, K]`` where ``fused_supported`` says so:
+        ``norm = (ssq, weight, eps)`` makes the input ``RMSNorm(x) * weight`` (``ssq``: per-tile sums of squares of
+        ``x``, as returned by the call that produced it); ``residual`` makes the result
+        ``(y + residual, ssq)``; ``silu_mul`` as ``forward_silu_mul``; ``peer`` as ``PeerAllReduce`` passes it."""
+        return _w4a16(x, self.qweight, self.qscales, self.qzeros, self.bias, None, silu_mul=silu_mul, peer=peer,
+                      norm=norm, residual=residual)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, "

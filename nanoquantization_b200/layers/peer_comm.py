@@ -72,6 +72,16 @@ class PeerAllReduce:
             M, N, _lib.dtype_code(dtype), _lib.stream_ptr()))
         return out
 
+    def fused_residual_supported(self, linear, M: int) -> bool:
+        return self.fused and self.world > 1 and linear.fused_supported(M, residual=True, world=self.world, slot_bytes=self.slot_bytes)
+
+    def linear_all_reduce_residual(self, linear, x: torch.Tensor, residual: torch.Tensor):
+        """``(all_reduce(linear(x)) + residual, per-tile sums of squares of that)`` in the linear's own two launches
+        (where ``fused_residual_supported``)."""
+        off = self._next * self.slot_bytes
+        self._next = (self._next + 1) % self.num_slots
+        return linear.forward_fused(x, residual=residual, peer=(self._ptrs, self.rank, self.world, off, self.slot_bytes))
+
     def linear_all_reduce(self, linear, x: torch.Tensor) -> torch.Tensor:
         """``all_reduce(linear(x))`` with the partial result written straight into peer-visible memory."""
         M, N = x.shape[0], linear.out_features

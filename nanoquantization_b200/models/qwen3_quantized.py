@@ -155,13 +155,24 @@ class Qwen3QuantizedAttention(nn.Module):
         o = o.transpose(1, 2).reshape(bs, -1, self.num_heads * self.head_dim)
         return _all_reduce(self.o_proj(o), self.tp_size, self.tp_group)
 
-    def forward_tokens(self, x: torch.Tensor, positions: torch.Tensor, attend: Callable) -> torch.Tensor:
+    def fusable(self, T: int) -> bool:
+        """Whether ``forward_tokens`` can take the input norm into q/k/v and the residual add into o_proj for T tokens."""
+        if self.qkv_proj is None or not self.qkv_proj.qweight.is_cuda or not self.qkv_proj.fused_supported(T, norm=True):
+            return False
+        if self.tp_size == 1:
+            return self.o_proj.fused_supported(T, residual=True)
+        return self.tp_comm is not None and self.tp_comm.fused_residual_supported(self.o_proj, T)
+
+    def forward_tokens(self, x: torch.Tensor, positions: torch.Tensor, attend: Callable, norm=None,
+                       residual: Optional[torch.Tensor] = None):
         """``x`` is ``[T, hidden]``; ``attend(q, k, v)`` stores k, v in its cache and returns ``[T, Hq, D]``
         (called with ``stored=True`` when this method already stored them through ``attend.kv_target``).
         One launch for q/k/v (when fused), one for QK-norm + rotary embedding."""
         T = x.shape[0]
         nq, nk = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
-        if self.qkv_proj is not None:
+        if norm is not None:  # x is the residual stream; its RMSNorm is taken inside the linear
+            qkv = self.qkv_proj.forward_fused(x, norm=norm)
+        elif self.qkv_proj is not None:
             qkv = self.qkv_proj(x)
         else:
             qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], dim=-1)
@@ -180,6 +191,10 @@ class Qwen3QuantizedAttention(nn.Module):
             q, k = self.rope(q, k, positions)
         v = qkv[:, nq + nk:].view(T, self.num_kv_heads, self.head_dim)
         o = (attend(q, k, v, stored=True) if stored else attend(q, k, v)).reshape(T, nq)
+        if residual is not None:  # (new residual stream, its per-tile sums of squares) from o_proj's own launches
+            if self.tp_size > 1:
+                return self.tp_comm.linear_all_reduce_residual(self.o_proj, o, residual)
+            return self.o_proj.forward_fused(o, residual=residual)
         return _row_parallel(self.o_proj, o, self.tp_size, self.tp_group, self.tp_comm)
 
 
@@ -214,9 +229,22 @@ class Qwen3QuantizedMLP(nn.Module):
             y1, y2 = self.gate_proj(x), self.up_proj(x)
         return _all_reduce(self.down_proj(F.silu(y1) * y2), self.tp_size, self.tp_group)
 
-    def forward_tokens(self, x: torch.Tensor) -> torch.Tensor:
+    def fusable(self, T: int) -> bool:
+        if (self.gate_up_proj is None or not self.gate_up_proj.qweight.is_cuda
+                or not self.gate_up_proj.fused_supported(T, norm=True, silu_mul=True)):
+            return False
+        if self.tp_size == 1:
+            return self.down_proj.fused_supported(T, residual=True)
+        return self.tp_comm is not None and self.tp_comm.fused_residual_supported(self.down_proj, T)
+
+    def forward_tokens(self, x: torch.Tensor, norm=None, residual: Optional[torch.Tensor] = None):
         if self.gate_up_proj is None:
             return self.forward(x)
+        if residual is not None:  # as in the attention: norm inside gate_up, residual add inside down_proj
+            y = self.gate_up_proj.forward_fused(x, norm=norm, silu_mul=True)
+            if self.tp_size > 1:
+                return self.tp_comm.linear_all_reduce_residual(self.down_proj, y, residual)
+            return self.down_proj.forward_fused(y, residual=residual)
         return _row_parallel(self.down_proj, self.gate_up_proj.forward_silu_mul(x), self.tp_size, self.tp_group, self.tp_comm)
 
 
@@ -229,17 +257,39 @@ class Qwen3QuantizedBlock(nn.Module):
         self.mlp = Qwen3QuantizedMLP(hidden_size, intermediate_size, w_bits, group_size, **kw)
         self.input_layernorm = RMSNorm(hidden_size, rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(hidden_size, rms_norm_eps)
+        self._fusable: dict[int, bool] = {}  # per token count: can the norms and residual adds go into the linears?
 
     def forward(self, x, position_ids):
         x = x + self.self_attn(self.input_layernorm(x), position_ids)
         return x + self.mlp(self.post_attention_layernorm(x))
 
-    def forward_tokens(self, x, residual, positions, attend):
-        """``x`` is the previous sub-layer's output still to be added to the residual stream."""
-        h, residual = fused.add_rmsnorm(x, residual, self.input_layernorm.weight, self.input_layernorm.eps)
-        a = self.self_attn.forward_tokens(h, positions, attend)
-        h, residual = fused.add_rmsnorm(a, residual, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps)
-        return self.mlp.forward_tokens(h), residual
+    def forward_tokens(self, x, residual, positions, attend, ssq=None):
+        """State between sub-layers: either ``x`` is a sub-layer output still to be added to ``residual`` (``ssq``
+        None), or ``x`` is None, ``residual`` is already the updated stream and ``ssq`` holds its per-tile sums of
+        squares.  The second form is what the decode-sized linears produce and consume themselves (norm taken
+        inside q/k/v and gate/up, residual add inside o_proj and down_proj): no launch for the norms.
+        Returns the same triple."""
+        T = residual.shape[0] if x is None else x.shape[0]
+        fuse = self._fusable.get(T)
+        if fuse is None:
+            fuse = self._fusable[T] = bool(T <= 16 and self.self_attn.fusable(T) and self.mlp.fusable(T))
+        if not fuse:
+            if x is None:  # a fused layer ahead of an unfused one does not happen (same shapes), but stay correct
+                h = fused.add_rmsnorm(residual, None, self.input_layernorm.weight, self.input_layernorm.eps)[0]
+            else:
+                h, residual = fused.add_rmsnorm(x, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+            a = self.self_attn.forward_tokens(h, positions, attend)
+            h, residual = fused.add_rmsnorm(a, residual, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps)
+            return self.mlp.forward_tokens(h), residual, None
+        if ssq is None:
+            h, residual = fused.add_rmsnorm(x, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+            residual, ssq = self.self_attn.forward_tokens(h, positions, attend, None, residual)
+        else:
+            residual, ssq = self.self_attn.forward_tokens(residual, positions, attend,
+                                                          (ssq, self.input_layernorm.weight, self.input_layernorm.eps), residual)
+        residual, ssq = self.mlp.forward_tokens(residual, (ssq, self.post_attention_layernorm.weight,
+                                                           self.post_attention_layernorm.eps), residual)
+        return None, residual, ssq
 
 
 class Qwen3QuantizedModel(nn.Module):
@@ -262,9 +312,11 @@ class Qwen3QuantizedModel(nn.Module):
         return self.norm(x)
 
     def forward_tokens(self, token_ids, positions, attend_for_layer: Callable[[int], Callable]):
-        x, residual = self.embed_tokens(token_ids), None
+        x, residual, ssq = self.embed_tokens(token_ids), None, None
         for i, layer in enumerate(self.layers):
-            x, residual = layer.forward_tokens(x, residual, positions, attend_for_layer(i))
+            x, residual, ssq = layer.forward_tokens(x, residual, positions, attend_for_layer(i), ssq)
+        if x is None:  # the last linear already added its output to the residual stream
+            return fused.add_rmsnorm(residual, None, self.norm.weight, self.norm.eps)[0]
         return fused.add_rmsnorm(x, residual, self.norm.weight, self.norm.eps)[0]
 
 
@@ -301,11 +353,13 @@ class Qwen3QuantizedForCausalLM(nn.Module):
         for layer in self.model.layers:
             layer.self_attn.tp_comm = comm
             layer.mlp.tp_comm = comm
+            layer._fusable.clear()
 
     def fuse_projections(self) -> None:
         for layer in self.model.layers:
             layer.self_attn.fuse_projections()
             layer.mlp.fuse_projections()
+            layer._fusable.clear()
 
     def forward(self, x, position_ids):
         return self.model(x, position_ids)

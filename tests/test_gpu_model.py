@@ -156,3 +156,38 @@ def test_gate_up_with_fused_activation_is_bit_identical_to_the_separate_steps(K,
     got = lin.forward_silu_mul(x)
     assert got.shape == (M, I) and torch.equal(got, want)
     assert torch.equal(lin.forward_silu_mul(x), want)  # and again: the workspace is left reusable
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [1, 5, 16])
+@torch.no_grad()
+def test_linears_with_norm_prologue_and_residual_epilogue(M, dtype):
+    """o_proj-like linear with the residual add inside (bit-identical to linear + add, and its sums of
+    squares), then a q/k/v-like linear that takes the RMSNorm of that stream inside (same roundings as
+    the separate norm; the mean of squares is added in a different order, hence a tolerance)."""
+    from nanoquantization_b200.layers import fused
+    import oracle.awq_oracle as O
+    H, Kin, Nout = 1024, 2048, 1536
+    a = O.make_case(Kin, H, M, group_size=128, dtype=dtype, seed=31)
+    b = O.make_case(H, Nout, M, group_size=128, dtype=dtype, seed=32)
+    lin_o = nq.WQLinear_GEMM(4, 128, Kin, H, DEV, False, dtype)
+    lin_q = nq.WQLinear_GEMM(4, 128, H, Nout, DEV, False, dtype)
+    for lin, c in ((lin_o, a), (lin_q, b)):
+        lin.qweight.copy_(c["qweight"]); lin.qscales.copy_(c["qscales"]); lin.qzeros.copy_(c["qzeros"])
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = a["x"].to(DEV)
+    res = torch.randn(M, H, generator=g, device=DEV).to(dtype)
+    w = (torch.rand(H, generator=g, device=DEV) + 0.5).to(dtype)
+    assert lin_o.fused_supported(M, residual=True) and lin_q.fused_supported(M, norm=True)
+    h, ssq = lin_o.forward_fused(x, residual=res)
+    assert torch.equal(h, lin_o(x) + res)
+    assert ssq.shape == (M, H // 512)
+    want_ss = (h.float() ** 2).sum(1)
+    assert float((ssq.sum(1) - want_ss).abs().max()) <= 1e-5 * float(want_ss.max())
+    got = lin_q.forward_fused(h, norm=(ssq, w, 1e-6))
+    want = lin_q(fused.add_rmsnorm(h, None, w, 1e-6)[0])
+    assert O.rel_err(got, want) <= 2e-3
+    # and both at once on one linear, twice (the workspace stays reusable)
+    for _ in range(2):
+        h2, ssq2 = lin_o.forward_fused(x, residual=res)
+        assert torch.equal(h2, h) and torch.equal(ssq2, ssq)

@@ -61,6 +61,15 @@ def _worker(rank, world, port, out):
         errs.append(0.0 if all(torch.equal(o, outs[0]) for o in outs2) else 1.0)
         errs.append(float(plain.status()))
         plain.close()
+        # ... and with the residual add of the block in the same launches
+        res = torch.randn(5, 512, generator=torch.Generator().manual_seed(3)).to(torch.float16).to(dev)
+        assert comm.fused_residual_supported(row.shard, 5)
+        for _ in range(3):
+            h, ssq = comm.linear_all_reduce_residual(row.shard, xs, res)
+            errs.append(0.0 if torch.equal(h, outs[0] + res) else 1.0)
+            want_ss = (h.float() ** 2).sum(1)
+            errs.append(float((ssq.sum(1) - want_ss).abs().max() / want_ss.max()))
+        errs.append(float(comm.status()))
         big = comm.linear_all_reduce(row.shard, torch.randn(600, 512, device=dev, dtype=torch.float16))  # too large: NCCL path
         assert big.shape == (600, 512)
         comm.close()
