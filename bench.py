@@ -284,13 +284,16 @@ def run_ours(args):
                           "kernel": lib.nqb200_gemm_kernel_name(M, n, k, GROUP, 0).decode()})
     clocks = sampler.stop() if rank == 0 else None
     barrier()
-    decode = None
+    decode, small = None, None
     if not args.no_decode:
         for k in list(layers):
             del layers[k]
         torch.cuda.empty_cache()
         decode = decode_bench(world, rank, dev, dtype)
         barrier()
+        if world == 1:
+            torch.cuda.empty_cache()
+            small = engine_bench_0p6b(dev, dtype)
 
     if rank == 0:
         pk = peaks()
@@ -342,7 +345,7 @@ def run_ours(args):
             "gpu_launches": args.steps * sum(lib.nqb200_gemm_launch_count(M, *shard_shape(*SHAPES[si], world)[::-1], GROUP, 0)
                                              for (si, M) in points),
             "roofline": roof_prefill, "roofline_decode": roof_decode,
-            "clocks": clocks, "points": per_point, "decode_qwen3_8b": decode,
+            "clocks": clocks, "points": per_point, "decode_qwen3_8b": decode, "engine_qwen3_0p6b": small,
         }
         if world == 1:
             line["cpu_baseline"] = cpu_baseline(seconds_budget=20.0)
@@ -360,6 +363,41 @@ def run_ours(args):
 # --------------------------------------------------------------------------
 # second half of the metric: Qwen3-8B-architecture AWQ decode tokens/s through the engine
 # --------------------------------------------------------------------------
+def engine_bench_0p6b(dev, dtype, prompts=32, prompt_len=512, steps=256):
+    """Random-init Qwen3-0.6B (w4 g128) on one GPU through LLMEngine.generate: 32 prompts of 512 random
+    ids, 256 greedy tokens each (prefill, then decode steps as CUDA graphs)."""
+    from nanoquantization_b200 import WQLinear_GEMM
+    from nanoquantization_b200.engine import LLMEngine
+    from nanoquantization_b200.models import QWEN3_SHAPES, Qwen3QuantizedForCausalLM
+    shp = QWEN3_SHAPES["qwen3-0.6b"]
+    model = Qwen3QuantizedForCausalLM(shp["num_hidden_layers"], 151936, shp["hidden_size"], shp["total_num_heads"],
+                                      shp["total_num_kv_heads"], 8192, shp["intermediate_size"], 4, GROUP, 128, False, 1e6,
+                                      1e-6, device=dev, dtype=dtype)
+    n = 0
+    for mod in model.modules():
+        if isinstance(mod, WQLinear_GEMM):
+            fill_layer(mod, 9000 + n, dev, dtype)
+            n += 1
+    torch.nn.init.normal_(model.model.embed_tokens.weight, std=0.02)
+    torch.nn.init.normal_(model.lm_head.weight, std=0.02)
+    model.fuse_projections()
+    block = 256
+    per_seq = -(-(prompt_len + steps + 8) // block)
+    eng = LLMEngine(model, num_blocks=prompts * per_seq + 4, block_size=block, max_batch=prompts)
+    g = torch.Generator().manual_seed(2)
+    ids = [torch.randint(0, 151936, (prompt_len,), generator=g).tolist() for _ in range(prompts)]
+    eng.generate(ids[:prompts], 4)  # warm-up: graphs captured, workspaces allocated
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = eng.generate(ids, steps)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    new = sum(len(o) for o in outs)
+    return {"model": "qwen3-0.6b-arch w4 g128 random init", "prompts": prompts, "prompt_len": prompt_len,
+            "new_tokens": new, "wall_s": round(dt, 3), "generated_tok_per_s": round(new / dt, 1),
+            "total_tok_per_s": round((new + prompts * prompt_len) / dt, 1)}
+
+
 def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, steps=16):
     """Random-init Qwen3-8B (w4 g128, tensor-parallel over `world` ranks), sequences with a
     2048-token context in the paged KV cache, greedy decode steps replayed as a CUDA graph."""
@@ -436,6 +474,28 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
         out["points"].append(pt)
         for s in seqs:
             eng.blocks.release(s)
+    # the configuration's 4096-token prefill: one sequence through the engine's prefill path
+    seq = Sequence(10 ** 6, torch.randint(0, 151936, (4096,), generator=g).tolist(), 1)
+    if eng.blocks.ensure(seq, 4096 + 8):
+        model.attach_peer_comm(None)
+        for _ in range(2):
+            eng._prefill([seq])
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            eng._prefill([seq])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 3
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        out["prefill_4096"] = {"ms": round(ms, 3), "tok_per_s": round(4096 / ms * 1e3, 1)}
+        eng.blocks.release(seq)
     if comm is not None:
         out["peer_allreduce_status"] = comm.status()
     del eng, model
