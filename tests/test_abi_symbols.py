@@ -53,6 +53,19 @@ def test_host_only_entry_points():
     assert lib.nqb200_gemm_launch_count(1, 512, 128, 128, 0) == 1
     assert lib.nqb200_gemm_launch_count(4096, 4096, 4096, 128, 0) == 1
     assert lib.nqb200_gemm_launch_count(0, 4096, 4096, 128, 0) == 0
+    # which decode fusions a shape takes (host-side decision, no GPU needed)
+    from nanoquantization_b200._lib import FUSE_ALLREDUCE, FUSE_RESIDUAL, FUSE_RMSNORM, FUSE_SILU_MUL
+    sup = lib.nqb200_gemm_decode_fused_supported
+    assert sup(1, 4096, 4096, 128, 0, FUSE_RMSNORM, 0, 0) == 1
+    assert sup(16, 4096, 12288, 128, 0, FUSE_RESIDUAL, 0, 0) == 1
+    assert sup(4, 24576, 4096, 128, 0, FUSE_RMSNORM | FUSE_SILU_MUL, 0, 0) == 1
+    assert sup(4, 24576, 4096, 128, 0, FUSE_SILU_MUL | FUSE_RESIDUAL, 0, 0) == 0      # not together
+    assert sup(17, 4096, 4096, 128, 0, FUSE_RMSNORM, 0, 0) == 0                        # decode sizes only
+    assert sup(1, 512, 128, 128, 0, FUSE_RESIDUAL, 0, 0) == 0                          # one CTA covers the tile's whole K
+    assert sup(4, 4096, 2048, 128, 0, FUSE_RESIDUAL | FUSE_ALLREDUCE, 2, 1 << 20) == 1
+    assert sup(4, 4096, 2048, 128, 0, FUSE_RESIDUAL | FUSE_ALLREDUCE, 2, 1 << 10) == 0  # slot too small for world * M * N * 2 bytes
+    assert lib.nqb200_gemm_gate_up_silu_supported(1, 6400, 5120, 128, 0) == 0           # I = 3200 is not tile-aligned
+    assert lib.nqb200_gemm_allreduce_supported(4, 4096, 2048, 128, 0, 9, 1 << 20) == 0   # more ranks than the buffer layout holds
 
 
 def test_library_is_not_older_than_its_sources():
