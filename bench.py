@@ -398,6 +398,62 @@ def engine_bench_0p6b(dev, dtype, prompts=32, prompt_len=512, steps=256):
             "total_tok_per_s": round((new + prompts * prompt_len) / dt, 1)}
 
 
+def serve_bench(world, rank, dev, dtype, requests=256, arch="qwen3-32b", max_batch=64):
+    """Continuous batching through LLMEngine.generate: random-init model of `arch` (w4 g128, tensor-parallel
+    over `world` ranks), `requests` requests with prompt lengths uniform in [128, 4096] and output lengths
+    uniform in [64, 512], random ids, greedy decoding (BASELINE.json's largest configuration names the
+    32B architecture at TP=8).  Not part of the default run: `bench.py --serve`."""
+    import torch.distributed as dist
+    from nanoquantization_b200 import WQLinear_GEMM
+    from nanoquantization_b200.engine import LLMEngine
+    from nanoquantization_b200.models import QWEN3_SHAPES, Qwen3QuantizedForCausalLM
+    shp = QWEN3_SHAPES[arch]
+    model = Qwen3QuantizedForCausalLM(shp["num_hidden_layers"], 151936, shp["hidden_size"], shp["total_num_heads"],
+                                      shp["total_num_kv_heads"], 8192, shp["intermediate_size"], 4, GROUP, 128, False, 1e6,
+                                      1e-6, tp_size=world, tp_rank=rank, device=dev, dtype=dtype)
+    n = 0
+    for mod in model.modules():
+        if isinstance(mod, WQLinear_GEMM):
+            fill_layer(mod, 7000 + n + 100 * rank, dev, dtype)
+            n += 1
+    torch.nn.init.normal_(model.model.embed_tokens.weight, std=0.02)
+    torch.nn.init.normal_(model.lm_head.weight, std=0.02)
+    model.fuse_projections()
+    comm = None
+    if world > 1:
+        from nanoquantization_b200.layers.peer_comm import PeerAllReduce
+        comm = PeerAllReduce(slot_bytes=2 << 20, num_slots=8)
+        model.attach_peer_comm(comm)
+    g = torch.Generator().manual_seed(11)   # the same requests on every rank
+    plen = torch.randint(128, 4097, (requests,), generator=g).tolist()
+    olen = torch.randint(64, 513, (requests,), generator=g).tolist()
+    prompts = [torch.randint(0, 151936, (n_,), generator=g).tolist() for n_ in plen]
+    block = 256
+    eng = LLMEngine(model, num_blocks=max_batch * (-(-(4096 + 512 + 8) // block)) + 4, block_size=block, max_batch=max_batch,
+                    max_prefill_tokens=8192)
+    eng.generate([p[:300] for p in prompts[:max_batch]], 3)   # warm-up: workspaces, first graphs
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    outs = eng.generate(prompts, olen)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    new = sum(len(o) for o in outs)
+    assert [len(o) for o in outs] == olen
+    out = {"workload": f"{arch}-arch w4 g128 random init, continuous batching", "tp": world, "requests": requests,
+           "prompt_tokens": sum(plen), "new_tokens": new, "max_batch": max_batch, "wall_s": round(dt, 2),
+           "generated_tok_per_s": round(new / dt, 1), "total_tok_per_s": round((new + sum(plen)) / dt, 1),
+           "decode_graphs": len(eng._graphs)}
+    if comm is not None:
+        out["peer_allreduce_status"] = comm.status()
+    return out
+
+
 def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, steps=16):
     """Random-init Qwen3-8B (w4 g128, tensor-parallel over `world` ranks), sequences with a
     2048-token context in the paged KV cache, greedy decode steps replayed as a CUDA graph."""
@@ -582,6 +638,29 @@ def run_reference(args):
     emit(json.dumps(line))
 
 
+def run_serve(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    out = serve_bench(world, rank, dev, dtype, requests=args.requests, arch=args.serve)
+    if rank == 0:
+        emit(json.dumps(out))
+    if world > 1:  # leave without the NCCL teardown that can hang after graph-captured collectives
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 def run_point(args):
     """One (M, K, N) point launched --reps times over rotating weight copies, timed with CUDA
     events; the small, single-kernel case profilers are pointed at."""
@@ -648,9 +727,14 @@ def main():
     ap.add_argument("--reps", type=int, default=6)
     ap.add_argument("--no-graph", action="store_true", help="with --point: plain launches (what a profiler should see)")
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
+    ap.add_argument("--serve", nargs="?", const="qwen3-32b", default=None,
+                    help="instead of the sweep: the continuous-batching workload on this architecture (tensor-parallel under torchrun)")
+    ap.add_argument("--requests", type=int, default=256)
     args = ap.parse_args()
     protect_stdout()
-    if args.point:
+    if args.serve:
+        run_serve(args)
+    elif args.point:
         run_point(args)
     elif args.impl == "reference":
         run_reference(args)

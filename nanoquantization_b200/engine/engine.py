@@ -15,7 +15,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Callable, Sequence as Seq
+from typing import Callable, Optional, Sequence as Seq
 
 import torch
 import torch.nn.functional as F
@@ -145,8 +145,10 @@ class LLMEngine:
         self.dtype = model.lm_head.weight.dtype
         self.kv_heads, self.q_heads, self.head_dim = attn.num_kv_heads, attn.num_heads, attn.head_dim
         self.block_size = block_size
-        self.cache = PagedKVCache(len(model.model.layers), num_blocks, block_size, self.kv_heads, self.head_dim,
+        # one block more than the allocator hands out: padding rows of a bucketed decode batch write there
+        self.cache = PagedKVCache(len(model.model.layers), num_blocks + 1, block_size, self.kv_heads, self.head_dim,
                                   self.dtype, self.device)
+        self.scratch_block = num_blocks
         self.blocks = BlockManager(num_blocks, block_size)
         self.scheduler = Scheduler(self.blocks, max_batch, max_prefill_tokens)
         self.use_cuda_graph = use_cuda_graph
@@ -221,16 +223,21 @@ class LLMEngine:
         last = torch.tensor([sum(lens[:i + 1]) - 1 for i in range(len(lens))], dtype=torch.long, device=dev)
         return self.model.greedy_tokens(h[last])
 
-    def _decode_inputs(self, batch: list[Sequence], max_blocks: int):
+    def _decode_inputs(self, batch: list[Sequence], max_blocks: int, rows: Optional[int] = None):
+        """Host tensors of one decode step.  ``rows`` > len(batch) pads the batch: a padding row is token 0 at
+        position 0 of a one-token sequence that lives in the scratch block."""
         B = len(batch)
-        toks = torch.tensor([(s.output or s.prompt)[-1] for s in batch], dtype=torch.long)
-        pos = torch.tensor([len(s) - 1 for s in batch], dtype=torch.long)
+        rows = B if rows is None else rows
+        pad = rows - B
+        toks = torch.tensor([(s.output or s.prompt)[-1] for s in batch] + [0] * pad, dtype=torch.long)
+        pos = torch.tensor([len(s) - 1 for s in batch] + [0] * pad, dtype=torch.long)
         slots = torch.tensor([s.blocks[(len(s) - 1) // self.block_size] * self.block_size + (len(s) - 1) % self.block_size
-                              for s in batch], dtype=torch.long)
-        bt = torch.zeros(B, max_blocks, dtype=torch.long)
+                              for s in batch] + [self.scratch_block * self.block_size] * pad, dtype=torch.long)
+        bt = torch.zeros(rows, max_blocks, dtype=torch.long)
         for i, s in enumerate(batch):
             bt[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.long)
-        ctx = torch.tensor([len(s) for s in batch], dtype=torch.long)
+        bt[B:, 0] = self.scratch_block
+        ctx = torch.tensor([len(s) for s in batch] + [1] * pad, dtype=torch.long)
         return toks, pos, slots, bt, ctx
 
     def _decode_forward(self, toks, pos, slots, bt, ctx, max_blocks):
@@ -245,10 +252,15 @@ class LLMEngine:
     def _decode(self, batch: list[Sequence]) -> torch.Tensor:
         B = len(batch)
         max_blocks = max(len(s.blocks) for s in batch)
-        host = self._decode_inputs(batch, max_blocks)
         if not self.use_cuda_graph:
+            host = self._decode_inputs(batch, max_blocks)
             return self._decode_forward(*(t.to(self.device) for t in host), max_blocks)
-        key = (B, max_blocks)
+        # one graph per (batch bucket, block-count bucket): batches are padded up to a power of two, block
+        # tables to a power of two of columns, so continuous batching replays a few dozen graphs
+        rows = 1 << (B - 1).bit_length()
+        max_blocks = 1 << (max_blocks - 1).bit_length()
+        host = self._decode_inputs(batch, max_blocks, rows)
+        key = (rows, max_blocks)
         if key not in self._graphs:
             static = [t.to(self.device) for t in host]
             side = torch.cuda.Stream()
@@ -265,7 +277,7 @@ class LLMEngine:
         for dst, src in zip(static, host):
             dst.copy_(src, non_blocking=True)
         graph.replay()
-        return out
+        return out[:B]
 
     # ----------------------------------------------------------------------- API
     def add_request(self, prompt: Seq[int], max_new_tokens: int) -> int:
