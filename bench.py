@@ -454,7 +454,7 @@ def serve_bench(world, rank, dev, dtype, requests=256, arch="qwen3-32b", max_bat
     return out
 
 
-def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, steps=16):
+def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, steps=16, prefill=True):
     """Random-init Qwen3-8B (w4 g128, tensor-parallel over `world` ranks), sequences with a
     2048-token context in the paged KV cache, greedy decode steps replayed as a CUDA graph."""
     import torch.distributed as dist
@@ -532,7 +532,7 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
             eng.blocks.release(s)
     # the configuration's 4096-token prefill: one sequence through the engine's prefill path
     seq = Sequence(10 ** 6, torch.randint(0, 151936, (4096,), generator=g).tolist(), 1)
-    if eng.blocks.ensure(seq, 4096 + 8):
+    if prefill and eng.blocks.ensure(seq, 4096 + 8):
         model.attach_peer_comm(None)
         for _ in range(2):
             eng._prefill([seq])
@@ -730,9 +730,15 @@ def main():
     ap.add_argument("--serve", nargs="?", const="qwen3-32b", default=None,
                     help="instead of the sweep: the continuous-batching workload on this architecture (tensor-parallel under torchrun)")
     ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--decode-only", type=int, default=0, metavar="BATCH",
+                    help="only the Qwen3-8B decode point of this batch size, 1 GPU (the case a launch list is taken of)")
     args = ap.parse_args()
     protect_stdout()
-    if args.serve:
+    if args.decode_only:
+        torch.cuda.set_device(0)
+        dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+        emit(json.dumps(decode_bench(1, 0, torch.device("cuda", 0), dtype, batches=(args.decode_only,), steps=4, prefill=False)))
+    elif args.serve:
         run_serve(args)
     elif args.point:
         run_point(args)
