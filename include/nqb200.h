@@ -1,7 +1,9 @@
 /* nqb200 -- C ABI of the B200 (sm_100a) AWQ W4A16 linear kernels.
  *
  * Every entry point takes plain device pointers and sizes; nothing here
- * allocates, frees or retains device memory, throws, aborts or traps.  All
+ * allocates, frees or retains device memory (except nqb200_comm_alloc /
+ * nqb200_comm_free / nqb200_comm_import, the one-time set-up of a
+ * tensor-parallel communication buffer), throws, aborts or traps.  All
  * functions returning int return NQB200_OK (0) or a nonzero status; the text
  * for a status comes from nqb200_status_string().
  *
@@ -191,6 +193,15 @@ int nqb200_comm_export(void* ptr, void* handle64);
 int nqb200_comm_import(const void* handle64, void** ptr);
 int nqb200_comm_unimport(void* ptr);
 size_t nqb200_comm_data_offset(void);
+/* How long this rank's all-reduce kernels wait for their peers before they give up (default one
+ * second); `own_buffer` is the rank's own nqb200_comm_alloc buffer.  Synchronous; call it between
+ * steps. */
+int nqb200_comm_set_wait_limit(void* own_buffer, uint64_t nanoseconds);
+/* Waits for `stream`, then returns what this rank's all-reduce kernels recorded in its own buffer:
+ * NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a wait for a peer ran out (the kernel then returned
+ * without writing its output: the result of that call, and of everything computed from it, is
+ * undefined and must be discarded).  The record is cleared. */
+int nqb200_comm_status(void* own_buffer, void* stream);
 /* A row-parallel linear and its all-reduce in one call, for decode-sized M: every rank calls it with
  * its shard (x [M, K/world], weights [K/world, N]); the kernel that finishes the GEMM stores the
  * rank's partial result (rounded to the 16-bit type) straight into the slot at `slot_offset` of

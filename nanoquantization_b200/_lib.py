@@ -52,6 +52,8 @@ SIGNATURES = {
     "nqb200_comm_import": (_int, [_vp, ctypes.POINTER(_vp)]),
     "nqb200_comm_unimport": (_int, [_vp]),
     "nqb200_comm_data_offset": (_sz, []),
+    "nqb200_comm_set_wait_limit": (_int, [_vp, ctypes.c_uint64]),
+    "nqb200_comm_status": (_int, [_vp, _vp]),
     "nqb200_gemm_allreduce_supported": (_int, [_i64, _i64, _i64, _i64, _int, _int, _sz]),
     "nqb200_gemm_allreduce": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, ctypes.POINTER(_vp), _int, _int, _sz, _sz, _vp]),
     "nqb200_peer_allreduce": (_int, [ctypes.POINTER(_vp), _int, _int, _sz, _vp, _vp, _int, _i64, _i64, _int, _vp]),

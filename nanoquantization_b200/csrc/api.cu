@@ -1,5 +1,7 @@
 // C ABI of the library: argument checks and kernel choice.  No allocation,
-// no exceptions, no global mutable state.
+// no exceptions; the only mutable state in the library is per-device set-up
+// flags (kernel attributes, the address of the fixed scratch array), each
+// guarded by a mutex.
 #include "common.cuh"
 #include "peer_layout.cuh"
 

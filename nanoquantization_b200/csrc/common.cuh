@@ -11,6 +11,7 @@ namespace nqb200 {
 
 constexpr int kNumSMs = 148;          // B200: 2 dies x 74 SMs
 constexpr int kCounterBytes = 1 << 16; // head of the workspace: tile-arrival counters
+constexpr int kMaxDevices = 64;        // per-device host-side state (kernel attributes, symbol addresses)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -577,10 +577,10 @@ stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot
   if (lin < pe.world) {
     st_flag(reinterpret_cast<uint32_t*>(pe.peers[lin] + kArOffFlags2) + (size_t)set * kMaxRanks + pe.rank, e);
     const uint32_t* ours = reinterpret_cast<const uint32_t*>(mine + kArOffFlags2) + (size_t)set * kMaxRanks + lin;
-    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long t0 = global_timer_ns(), limit = peer_wait_limit_ns(mine);
     uint32_t it = 0;
     while ((int32_t)(ld_flag(ours) - e) < 0) {  // a rank already one call ahead shows e + 1
-      if ((++it & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) {
+      if ((++it & 255u) == 0 && global_timer_ns() - t0 > limit) {
         atomicExch(reinterpret_cast<int*>(mine), NQB200_ERR_WAIT_TIMEOUT);
         s_ok = 0;
         break;
@@ -611,8 +611,14 @@ stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot
 // that all of it is resident at once.
 template <int MT, bool BF16>
 static int stream_ctas_per_sm() {
-  static int occ = -1;
-  if (occ < 0) {
+  // measured once per device (the attributes set here belong to the device that is current)
+  static std::mutex mu;
+  static int occ[kMaxDevices];
+  static bool known[kMaxDevices] = {false};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return 0; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[dev]) {
     constexpr int kStreamSmem = StreamCfg<MT>::kSmem;
     int n = 0;
     int n2 = 0;
@@ -626,9 +632,10 @@ static int stream_ctas_per_sm() {
       return 0;
     }
     if (n2 < n) n = n2;
-    occ = n < StreamCfg<MT>::kCtasPerSm ? n : StreamCfg<MT>::kCtasPerSm;
+    occ[dev] = n < StreamCfg<MT>::kCtasPerSm ? n : StreamCfg<MT>::kCtasPerSm;
+    known[dev] = true;
   }
-  return occ;
+  return occ[dev];
 }
 
 template <int MT, bool BF16>
@@ -753,7 +760,6 @@ namespace nqb200 {
 // counters + two slots for each of the 296 CTAs of the 8-token configuration (the 16-token
 // configuration needs the same: 148 CTAs with slots twice the size)
 constexpr size_t kNoAllocScratchBytes = (size_t)kCounterBytes + (size_t)2 * kNumSMs * 2 * 8 * kUnitN * sizeof(float);
-constexpr int kMaxDevices = 64;
 }  // namespace nqb200
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[nqb200::kNoAllocScratchBytes];

@@ -40,6 +40,7 @@
 #include "common.cuh"
 #include "tma_utils.cuh"
 #include "umma_utils.cuh"
+#include <mutex>
 
 namespace nqb200 {
 namespace pre {
@@ -349,13 +350,20 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 template <bool BF16>
 static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx,
                     const Params& sp, int ctas, cudaStream_t st) {
-  static bool configured = false;  // idempotent attribute; a repeated set from two threads is harmless
-  if (!configured) {
-    if (cudaFuncSetAttribute(umma_prefill_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
-      cudaGetLastError();
-      return NQB200_ERR_LAUNCH;
+  // The shared-memory attribute belongs to the device that is current when it is set: one flag per device.
+  static std::mutex mu;
+  static bool configured[kMaxDevices] = {false};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return NQB200_ERR_UNSUPPORTED_DEVICE; }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!configured[dev]) {
+      if (cudaFuncSetAttribute(umma_prefill_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return NQB200_ERR_LAUNCH;
+      }
+      configured[dev] = true;
     }
-    configured = true;
   }
   const int rc = launch_overlapped(umma_prefill_kernel<BF16>, dim3(ctas), dim3(kThreads), kSmem, st, tw, ts, tz, tx, sp);
   if (rc != NQB200_OK || sp.ksplit <= 1) return rc;

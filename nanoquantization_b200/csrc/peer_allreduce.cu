@@ -13,8 +13,10 @@
 // device memory and is advanced by the kernel itself, so the kernel can be
 // replayed from a CUDA graph.
 //
-// Waits are bounded (about one second): on expiry the kernel records
-// NQB200_ERR_WAIT_TIMEOUT in the rank's status word and returns without hanging.
+// Waits are bounded (one second unless nqb200_comm_set_wait_limit says otherwise): on
+// expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in the rank's status word and returns
+// without hanging and without writing `out`; the host must read the status
+// (nqb200_comm_status) before it trusts the result.
 // Only plain peer loads and stores are used: no multimem, no TMA.
 #include "common.cuh"
 #include "tma_utils.cuh"
@@ -57,11 +59,11 @@ __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const ArPara
     st_flag(theirs, e);
     // wait for peer threadIdx.x's announcement in our buffer
     const uint32_t* ours = reinterpret_cast<const uint32_t*>(mine + kArOffFlags) + blockIdx.x * kMaxRanks + threadIdx.x;
-    const unsigned long long t0 = global_timer_ns();
+    const unsigned long long t0 = global_timer_ns(), limit = peer_wait_limit_ns(mine);
     uint32_t it = 0;
     // flags only grow; a peer that is already one call ahead shows e + 1
     while ((int32_t)(ld_flag(ours) - e) < 0) {
-      if ((++it & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) {
+      if ((++it & 255u) == 0 && global_timer_ns() - t0 > limit) {
         atomicExch(reinterpret_cast<int*>(mine), NQB200_ERR_WAIT_TIMEOUT);
         s_ok = 0;
         break;
@@ -125,6 +127,27 @@ extern "C" int nqb200_comm_import(const void* handle64, void** ptr) {
 }
 extern "C" int nqb200_comm_unimport(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? NQB200_OK : NQB200_ERR_LAUNCH; }
 extern "C" size_t nqb200_comm_data_offset(void) { return kArOffData; }
+extern "C" int nqb200_comm_set_wait_limit(void* own_buffer, uint64_t nanoseconds) {
+  if (!own_buffer) return NQB200_ERR_NULL_POINTER;
+  const unsigned long long v = nanoseconds;
+  if (cudaMemcpy((char*)own_buffer + kArOffWaitNs, &v, sizeof(v), cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaGetLastError();
+    return NQB200_ERR_LAUNCH;
+  }
+  return NQB200_OK;
+}
+extern "C" int nqb200_comm_status(void* own_buffer, void* stream) {
+  if (!own_buffer) return NQB200_ERR_NULL_POINTER;
+  int v = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(&v, own_buffer, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaGetLastError();
+    return NQB200_ERR_LAUNCH;
+  }
+  if (v != 0 && cudaMemsetAsync(own_buffer, 0, sizeof(int), st) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  return v;
+}
 
 extern "C" int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int world, size_t slot_offset, void* out,
                                      const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype, void* stream) {

@@ -4,9 +4,10 @@ manager, continuous-batching scheduler, model runner with CUDA-graph decode.
 The reference has none of this (its only execution is a full-sequence forward
 for a loss, models/qwen3_quantized.py:326-341); it exists so that the W4A16
 linears can be measured where they are used: prefill of batched prompts and
-greedy decode steps over a KV cache.  Attention is not the subject here and
-goes through PyTorch's scaled_dot_product_attention: per prompt at prefill,
-over the gathered pages of each sequence at decode.
+greedy decode steps over a KV cache.  Attention is not the subject here: at
+prefill it is PyTorch's scaled_dot_product_attention per prompt; at decode it is
+flash_attn's paged-KV kernel when that library loads on this GPU, else
+scaled_dot_product_attention over the gathered pages of each sequence.
 
 Layout: per layer two tensors ``[num_blocks, block_size, kv_heads, head_dim]``;
 a sequence owns a list of blocks; ``slot = block * block_size + offset``.
@@ -154,7 +155,9 @@ class LLMEngine:
         self.use_cuda_graph = use_cuda_graph
         self.paged_attention = self._probe_flash_attn() if block_size % 256 == 0 else None
         self._graphs: dict[tuple[int, int], tuple] = {}
+        self._warm_stream = None  # one side stream for every graph warm-up (scratch buffers are kept per stream)
         self._next_id = 0
+        self.max_tokens_per_sequence = num_blocks * block_size
 
     # ------------------------------------------------------------------ attention
     def _probe_flash_attn(self):
@@ -263,7 +266,9 @@ class LLMEngine:
         key = (rows, max_blocks)
         if key not in self._graphs:
             static = [t.to(self.device) for t in host]
-            side = torch.cuda.Stream()
+            if self._warm_stream is None:
+                self._warm_stream = torch.cuda.Stream()
+            side = self._warm_stream
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 self._decode_forward(*static, max_blocks)      # warm up outside the capture
@@ -281,6 +286,9 @@ class LLMEngine:
 
     # ----------------------------------------------------------------------- API
     def add_request(self, prompt: Seq[int], max_new_tokens: int) -> int:
+        if len(prompt) + 1 > self.max_tokens_per_sequence:
+            raise ValueError(f"a prompt of {len(prompt)} tokens can never be admitted: the KV cache holds "
+                             f"{self.max_tokens_per_sequence} tokens in all")
         sid = self._next_id
         self._next_id += 1
         self.scheduler.add(Sequence(sid, list(prompt), max_new_tokens))
@@ -289,12 +297,27 @@ class LLMEngine:
     def step(self) -> list[Sequence]:
         kind, batch = self.scheduler.step()
         if not batch:
+            if self.scheduler.waiting and not self.scheduler.running:
+                raise RuntimeError("the head of the waiting queue cannot be admitted although nothing is running "
+                                   "(the KV cache is too small for it)")
             return []
         new = (self._prefill(batch) if kind == "prefill" else self._decode(batch)).tolist()
+        self._check_device_status()
         for s, t in zip(batch, new):
             s.output.append(int(t))
             s.prefilled = True
         return self.scheduler.finish_step(kind, batch)
+
+    def _check_device_status(self) -> None:
+        """After the step's results reached the host: raise if a bounded device-side wait gave up during it
+        (a peer that never arrived at an all-reduce, a pipeline barrier inside a GEMM).  Such a kernel
+        returns without writing its output, so the step's tokens would be garbage."""
+        from .. import _lib
+        comm = getattr(self.model, "tp_comm", None)
+        if comm is not None:
+            comm.check()
+        if self.device.type == "cuda":
+            _lib.check_workspaces()
 
     def generate(self, prompts: Seq[Seq[int]], max_new_tokens) -> list[list[int]]:
         if isinstance(max_new_tokens, int):

@@ -25,9 +25,16 @@ class _DevicePtr:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+def _local(linear, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The rank's own partial product: the plain module forward, also for a row-parallel class
+    (whose ``forward`` would reduce again)."""
+    from .gemm import WQLinear_GEMM
+    return WQLinear_GEMM.forward(linear, x, out)
+
+
 class PeerAllReduce:
     def __init__(self, group=None, slot_bytes: int = 1 << 20, num_slots: int = 8, fused: bool = True,
-                 max_message_bytes: int = 192 << 10):
+                 max_message_bytes: int = 192 << 10, wait_limit_s: float = 1.0):
         assert num_slots >= 3
         self.fused = fused  # reduce inside the GEMM's finishing kernel where the library supports it
         # larger messages go through NCCL: measured at 8 ranks, a 512 KB message takes 1.4x longer here
@@ -54,6 +61,7 @@ class PeerAllReduce:
                 _lib.check(lib.nqb200_comm_import(ctypes.create_string_buffer(h, 64), ctypes.byref(p)))
                 self._ptrs[r] = p.value
                 self._imported.append(p.value)
+        _lib.check(lib.nqb200_comm_set_wait_limit(self._own, int(wait_limit_s * 1e9)))
         self._data_off = lib.nqb200_comm_data_offset()
         self._bytes = torch.as_tensor(_DevicePtr(self._own + self._data_off, slot_bytes * num_slots), device=self.device)
         dist.barrier(group=group)
@@ -89,9 +97,9 @@ class PeerAllReduce:
         """``all_reduce(linear(x))`` with the partial result written straight into peer-visible memory."""
         M, N = x.shape[0], linear.out_features
         if self.world == 1:
-            return linear(x)
+            return _local(linear, x)
         if not self.fits(M, N):
-            y = linear(x)
+            y = _local(linear, x)
             dist.all_reduce(y, group=self.group)
             return y
         dtype = linear.qscales.dtype
@@ -104,14 +112,17 @@ class PeerAllReduce:
             return _w4a16(x, linear.qweight, linear.qscales, linear.qzeros, linear.bias, None,
                           peer=(self._ptrs, self.rank, self.world, off, self.slot_bytes))
         slot, off = self.next_slot(M, N, linear.qscales.dtype)
-        linear(x, out=slot)
+        _local(linear, x, slot)
         return self.reduce(off, M, N, linear.qscales.dtype)
 
     def status(self) -> int:
-        """0, or the code a bounded wait recorded when it gave up (synchronises)."""
-        torch.cuda.synchronize()
-        word = torch.as_tensor(_DevicePtr(self._own, 4), device=self.device).view(torch.int32)
-        return int(word.item())
+        """0, or the code a bounded wait recorded when it gave up (waits for the current stream; the
+        record is cleared).  After a give-up the kernel has not written its output."""
+        return int(_lib.load().nqb200_comm_status(self._own, _lib.stream_ptr()))
+
+    def check(self) -> None:
+        """Raise if a wait for a peer ran out since the last check."""
+        _lib.check(self.status())
 
     def close(self) -> None:
         lib = _lib.load()

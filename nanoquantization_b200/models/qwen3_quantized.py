@@ -6,9 +6,10 @@ MLP :105-152, block :155-215, model :218-273, causal LM :276-341), so a
 reference checkpoint's keys (``model.layers.{i}.self_attn.q_proj.qweight`` ...)
 load by name.  Differences, all additive:
 
-* ``tp_size`` / ``tp_rank``: every linear is built with this rank's shard shape
-  (q/k/v/gate/up split along output columns by whole heads, o/down along input
-  rows on group boundaries) and the row-parallel outputs are all-reduced;
+* ``tp_size`` / ``tp_rank``: every linear is one of the tensor-parallel classes of
+  ``layers/parallel.py`` holding this rank's shard (q/k/v/gate/up column-parallel
+  by whole heads, o/down row-parallel on group boundaries); the row-parallel
+  classes do the all-reduce (NCCL, or peer memory once ``attach_peer_comm``);
 * besides the reference's full-sequence ``forward(x, position_ids)`` (causal
   SDPA, no cache) there is ``forward_tokens`` for a serving engine: flattened
   tokens, attention delegated to a callable that owns the paged KV cache;
@@ -27,7 +28,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..layers import fused
-from ..layers.gemm import WQLinear_GEMM
+from ..layers.gemm import WQLinear_GEMM  # noqa: F401  (the class every projection derives from)
+from ..layers.parallel import ColumnParallelWQLinear, MergedColumnParallelWQLinear, RowParallelWQLinear
 
 
 @dataclass
@@ -89,20 +91,6 @@ class RotaryCache(nn.Module):
         return self._rotate(q, cos, sin), self._rotate(k, cos, sin)
 
 
-def _all_reduce(t: torch.Tensor, tp_size: int, group) -> torch.Tensor:
-    if tp_size > 1:
-        dist.all_reduce(t, group=group)
-    return t
-
-
-def _row_parallel(linear, x: torch.Tensor, tp_size: int, group, comm) -> torch.Tensor:
-    """A row-parallel linear and its all-reduce: through the peer-memory kernel when a
-    ``PeerAllReduce`` is attached (decode-sized messages), else NCCL."""
-    if comm is not None and x.dim() == 2:
-        return comm.linear_all_reduce(linear, x)
-    return _all_reduce(linear(x), tp_size, group)
-
-
 class Qwen3QuantizedAttention(nn.Module):
     def __init__(self, hidden_size, total_num_heads, total_num_kv_heads, max_position_embeddings, w_bits=4,
                  group_size=128, head_dim=None, rope_theta=10000, rms_norm_eps=1e-6, *, tp_size=1, tp_rank=0,
@@ -114,24 +102,19 @@ class Qwen3QuantizedAttention(nn.Module):
         self.num_heads, self.num_kv_heads = total_num_heads // tp_size, total_num_kv_heads // tp_size
         self.tp_size, self.tp_group = tp_size, tp_group
         self.rope = RotaryCache(self.head_dim, max_position_embeddings, rope_theta)
-        mk = lambda k, n: WQLinear_GEMM(w_bits, group_size, k, n, device, False, dtype)  # noqa: E731
-        self.q_proj = mk(hidden_size, self.num_heads * self.head_dim)
-        self.k_proj = mk(hidden_size, self.num_kv_heads * self.head_dim)
-        self.v_proj = mk(hidden_size, self.num_kv_heads * self.head_dim)
-        self.o_proj = mk(self.num_heads * self.head_dim, hidden_size)
+        col = lambda n: ColumnParallelWQLinear(w_bits, group_size, hidden_size, n, tp_size, tp_rank, device, False, dtype,  # noqa: E731
+                                               process_group=tp_group)
+        self.q_proj = col(total_num_heads * self.head_dim)
+        self.k_proj = col(total_num_kv_heads * self.head_dim)
+        self.v_proj = col(total_num_kv_heads * self.head_dim)
+        self.o_proj = RowParallelWQLinear(w_bits, group_size, total_num_heads * self.head_dim, hidden_size, tp_size, tp_rank,
+                                          device, False, dtype, process_group=tp_group)
         self.q_norm = RMSNorm(self.head_dim, rms_norm_eps)
         self.k_norm = RMSNorm(self.head_dim, rms_norm_eps)
         self.qkv_proj = None
-        self.tp_comm = None  # a PeerAllReduce, attached by attach_peer_comm()
 
     def fuse_projections(self):
-        q, k, v = self.q_proj, self.k_proj, self.v_proj
-        m = WQLinear_GEMM(q.w_bits, q.group_size, q.in_features, q.out_features + k.out_features + v.out_features,
-                          q.qweight.device, False, q.qscales.dtype)
-        m.qweight = torch.cat([q.qweight, k.qweight, v.qweight], dim=1).contiguous()
-        m.qscales = torch.cat([q.qscales, k.qscales, v.qscales], dim=1).contiguous()
-        m.qzeros = torch.cat([q.qzeros, k.qzeros, v.qzeros], dim=1).contiguous()
-        self.qkv_proj = m
+        self.qkv_proj = MergedColumnParallelWQLinear.from_shards([self.q_proj, self.k_proj, self.v_proj])
         self.q_proj = self.k_proj = self.v_proj = None
 
     def _qkv(self, x):
@@ -153,15 +136,13 @@ class Qwen3QuantizedAttention(nn.Module):
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                                            enable_gqa=self.num_heads != self.num_kv_heads)
         o = o.transpose(1, 2).reshape(bs, -1, self.num_heads * self.head_dim)
-        return _all_reduce(self.o_proj(o), self.tp_size, self.tp_group)
+        return self.o_proj(o)
 
     def fusable(self, T: int) -> bool:
         """Whether ``forward_tokens`` can take the input norm into q/k/v and the residual add into o_proj for T tokens."""
         if self.qkv_proj is None or not self.qkv_proj.qweight.is_cuda or not self.qkv_proj.fused_supported(T, norm=True):
             return False
-        if self.tp_size == 1:
-            return self.o_proj.fused_supported(T, residual=True)
-        return self.tp_comm is not None and self.tp_comm.fused_residual_supported(self.o_proj, T)
+        return self.o_proj.residual_fusable(T)
 
     def forward_tokens(self, x: torch.Tensor, positions: torch.Tensor, attend: Callable, norm=None,
                        residual: Optional[torch.Tensor] = None):
@@ -192,10 +173,8 @@ class Qwen3QuantizedAttention(nn.Module):
         v = qkv[:, nq + nk:].view(T, self.num_kv_heads, self.head_dim)
         o = (attend(q, k, v, stored=True) if stored else attend(q, k, v)).reshape(T, nq)
         if residual is not None:  # (new residual stream, its per-tile sums of squares) from o_proj's own launches
-            if self.tp_size > 1:
-                return self.tp_comm.linear_all_reduce_residual(self.o_proj, o, residual)
-            return self.o_proj.forward_fused(o, residual=residual)
-        return _row_parallel(self.o_proj, o, self.tp_size, self.tp_group, self.tp_comm)
+            return self.o_proj.forward_residual(o, residual)
+        return self.o_proj(o)
 
 
 class Qwen3QuantizedMLP(nn.Module):
@@ -205,21 +184,16 @@ class Qwen3QuantizedMLP(nn.Module):
         assert intermediate_size % tp_size == 0 and (intermediate_size // tp_size) % group_size == 0
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size // tp_size
         self.tp_size, self.tp_group = tp_size, tp_group
-        mk = lambda k, n: WQLinear_GEMM(w_bits, group_size, k, n, device, False, dtype)  # noqa: E731
-        self.up_proj = mk(hidden_size, self.intermediate_size)
-        self.gate_proj = mk(hidden_size, self.intermediate_size)
-        self.down_proj = mk(self.intermediate_size, hidden_size)
+        col = lambda: ColumnParallelWQLinear(w_bits, group_size, hidden_size, intermediate_size, tp_size, tp_rank, device,  # noqa: E731
+                                             False, dtype, process_group=tp_group)
+        self.up_proj = col()
+        self.gate_proj = col()
+        self.down_proj = RowParallelWQLinear(w_bits, group_size, intermediate_size, hidden_size, tp_size, tp_rank, device,
+                                             False, dtype, process_group=tp_group)
         self.gate_up_proj = None
-        self.tp_comm = None
 
     def fuse_projections(self):
-        g, u = self.gate_proj, self.up_proj
-        m = WQLinear_GEMM(g.w_bits, g.group_size, g.in_features, g.out_features + u.out_features, g.qweight.device, False,
-                          g.qscales.dtype)
-        m.qweight = torch.cat([g.qweight, u.qweight], dim=1).contiguous()
-        m.qscales = torch.cat([g.qscales, u.qscales], dim=1).contiguous()
-        m.qzeros = torch.cat([g.qzeros, u.qzeros], dim=1).contiguous()
-        self.gate_up_proj = m
+        self.gate_up_proj = MergedColumnParallelWQLinear.from_shards([self.gate_proj, self.up_proj])
         self.gate_proj = self.up_proj = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -227,25 +201,21 @@ class Qwen3QuantizedMLP(nn.Module):
             y1, y2 = self.gate_up_proj(x).chunk(2, dim=-1)
         else:
             y1, y2 = self.gate_proj(x), self.up_proj(x)
-        return _all_reduce(self.down_proj(F.silu(y1) * y2), self.tp_size, self.tp_group)
+        return self.down_proj(F.silu(y1) * y2)
 
     def fusable(self, T: int) -> bool:
         if (self.gate_up_proj is None or not self.gate_up_proj.qweight.is_cuda
                 or not self.gate_up_proj.fused_supported(T, norm=True, silu_mul=True)):
             return False
-        if self.tp_size == 1:
-            return self.down_proj.fused_supported(T, residual=True)
-        return self.tp_comm is not None and self.tp_comm.fused_residual_supported(self.down_proj, T)
+        return self.down_proj.residual_fusable(T)
 
     def forward_tokens(self, x: torch.Tensor, norm=None, residual: Optional[torch.Tensor] = None):
         if self.gate_up_proj is None:
             return self.forward(x)
         if residual is not None:  # as in the attention: norm inside gate_up, residual add inside down_proj
             y = self.gate_up_proj.forward_fused(x, norm=norm, silu_mul=True)
-            if self.tp_size > 1:
-                return self.tp_comm.linear_all_reduce_residual(self.down_proj, y, residual)
-            return self.down_proj.forward_fused(y, residual=residual)
-        return _row_parallel(self.down_proj, self.gate_up_proj.forward_silu_mul(x), self.tp_size, self.tp_group, self.tp_comm)
+            return self.down_proj.forward_residual(y, residual)
+        return self.down_proj(self.gate_up_proj.forward_silu_mul(x))
 
 
 class Qwen3QuantizedBlock(nn.Module):
@@ -328,6 +298,7 @@ class Qwen3QuantizedForCausalLM(nn.Module):
         super().__init__()
         kw = dict(tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, device=device, dtype=dtype)
         self.tp_size, self.tp_rank, self.tp_group = tp_size, tp_rank, tp_group
+        self.tp_comm = None  # a PeerAllReduce, attached by attach_peer_comm()
         self.model = Qwen3QuantizedModel(num_hidden_layers, vocab_size, hidden_size, total_num_heads, total_num_kv_heads,
                                          max_position_embeddings, intermediate_size, w_bits, group_size, head_dim,
                                          rope_theta, rms_norm_eps, **kw)
@@ -350,9 +321,10 @@ class Qwen3QuantizedForCausalLM(nn.Module):
 
     def attach_peer_comm(self, comm) -> None:
         """Route the all-reduces after o_proj and down_proj through a ``PeerAllReduce``."""
+        self.tp_comm = comm
         for layer in self.model.layers:
-            layer.self_attn.tp_comm = comm
-            layer.mlp.tp_comm = comm
+            layer.self_attn.o_proj.attach_comm(comm)
+            layer.mlp.down_proj.attach_comm(comm)
             layer._fusable.clear()
 
     def fuse_projections(self) -> None:

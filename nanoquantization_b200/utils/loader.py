@@ -111,10 +111,13 @@ def load_model(model: nn.Module, path: str, *, tp_size: Optional[int] = None, tp
 
 
 def save_model(model: nn.Module, path: str, *, config: Optional[dict] = None, w_bits: int = 4, group_size: int = 128,
-               zero_point: bool = True) -> None:
-    """Write an unsharded (``tp_size == 1``), unfused model in the reference's layout: ``model.safetensors`` with the
-    ``state_dict`` keys and, if ``config`` (the Hugging Face config as a dict) is given, ``config.json`` with the
-    ``quantization_config`` block of ``scripts/qwen3_0pt6_billion.py:215-235``."""
+               zero_point: bool = True, calibration: Optional[dict] = None) -> None:
+    """Write an unsharded (``tp_size == 1``), unfused model in the reference's layout
+    (``scripts/qwen3_0pt6_billion.py:188-235``): ``model.safetensors`` with the ``state_dict`` keys,
+    ``model.safetensors.index.json`` mapping every key to that file (:202-207) and, if ``config`` (the Hugging
+    Face config as a dict) is given, ``config.json`` with the ``quantization_config`` block (:215-228).
+    ``calibration`` is that block's ``calibration`` entry (``dataset``, ``dataset_subset``, ``n_samples``,
+    ``max_seq_len``, ``apply_clip``); it is written when given."""
     from safetensors.torch import save_file
 
     if int(getattr(model, "tp_size", 1)) != 1:
@@ -122,10 +125,16 @@ def save_model(model: nn.Module, path: str, *, config: Optional[dict] = None, w_
     os.makedirs(path, exist_ok=True)
     # tied tensors are written under both names, as the reference's writer does
     tensors = {k: v.detach().to("cpu").contiguous().clone() for k, v in model.state_dict().items()}
-    save_file(tensors, os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
+    save_file(tensors, os.path.join(path, "model.safetensors"))
+    index = {"metadata": {"format": "pt"}, "weight_map": {k: "model.safetensors" for k in tensors}}
+    with open(os.path.join(path, "model.safetensors.index.json"), "w") as fh:
+        json.dump(index, fh, indent=2)
     if config is not None:
         cfg = dict(config)
-        cfg["quantization_config"] = {"quant_method": "awq", "w_bits": w_bits, "group_size": group_size,
-                                      "zero_point": zero_point, "version": "gemm", "modules_to_not_convert": []}
+        quant = {"quant_method": "awq", "w_bits": w_bits, "group_size": group_size, "zero_point": zero_point,
+                 "version": "gemm", "modules_to_not_convert": []}
+        if calibration is not None:
+            quant["calibration"] = dict(calibration)
+        cfg["quantization_config"] = quant
         with open(os.path.join(path, "config.json"), "w") as fh:
             json.dump(cfg, fh, indent=2)

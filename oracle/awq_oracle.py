@@ -85,6 +85,19 @@ def dequantize(qweight, qscales: torch.Tensor, qzeros) -> torch.Tensor:
     return d * s.repeat_interleave(g, dim=0)
 
 
+def dequantize_threaded(qweight: torch.Tensor, qscales: torch.Tensor, qzeros: torch.Tensor) -> torch.Tensor:
+    """``dequantize`` with torch CPU ops only, so that it runs on all host threads (numpy's shifts
+    and masks run on one).  Same arithmetic and citations: shift table gemm.py:64-69, integer
+    difference first and one multiply in the scale dtype gemm.py:112, 303-304.  This is the form the
+    benchmark's CPU baseline times; ``tests/test_oracle_golden.py`` checks it equals ``dequantize``."""
+    sh = torch.tensor(AWQ_SHIFTS, dtype=torch.int32)
+    q = ((qweight.unsqueeze(-1) >> sh) & 0xF).reshape(qweight.shape[0], -1)       # arithmetic shift, then mask: bits 0..3
+    z = ((qzeros.unsqueeze(-1) >> sh) & 0xF).reshape(qzeros.shape[0], -1)
+    g = q.shape[0] // z.shape[0]
+    diff = (q.view(z.shape[0], g, -1) - z.unsqueeze(1)).to(qscales.dtype)
+    return (diff * qscales.unsqueeze(1)).reshape(q.shape[0], -1)
+
+
 def w4a16_ref(x: torch.Tensor, qweight, qscales: torch.Tensor, qzeros,
               bias: torch.Tensor | None = None) -> torch.Tensor:
     """fp32 answer of the linear: ``x.float() @ dequantize(...).float() (+ bias)``.

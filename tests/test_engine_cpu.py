@@ -48,3 +48,15 @@ def test_scheduler_preempts_when_blocks_run_out():
     kind, batch = sch.step()          # both need a third block, none is free: the youngest is preempted
     assert kind == "decode" and [s.seq_id for s in batch] == [0]
     assert sch.waiting[0].seq_id == 1 and sch.waiting[0].prompt == [1] * 7 + [5] and sch.waiting[0].blocks == []
+
+
+def test_engine_rejects_a_prompt_the_cache_can_never_hold():
+    import pytest
+    import torch
+    from nanoquantization_b200.engine import LLMEngine
+    from nanoquantization_b200.models.qwen3_quantized import Qwen3QuantizedForCausalLM
+    model = Qwen3QuantizedForCausalLM(1, 64, 128, 2, 1, 32, 128, 4, 128, 64, device="cpu", dtype=torch.float16)
+    eng = LLMEngine(model, num_blocks=2, block_size=4, max_batch=2, use_cuda_graph=False)
+    with pytest.raises(ValueError, match="never be admitted"):
+        eng.add_request([1] * 8, 4)       # 8 prompt tokens + 1 generated > 2 blocks of 4
+    assert eng.add_request([1] * 7, 1) == 0

@@ -191,3 +191,34 @@ def test_linears_with_norm_prologue_and_residual_epilogue(M, dtype):
     for _ in range(2):
         h2, ssq2 = lin_o.forward_fused(x, residual=res)
         assert torch.equal(h2, h) and torch.equal(ssq2, ssq)
+
+
+@pytest.mark.parametrize("dtype,M", [(torch.bfloat16, 16), (torch.float16, 7)])
+@torch.no_grad()
+def test_fused_decode_block_vs_oracle(dtype, M):
+    """o_proj with the residual add inside, then a merged gate|up linear that takes the RMSNorm of that
+    stream and applies silu(gate) * up, against the CPU oracle's arithmetic for the same steps."""
+    import oracle.awq_oracle as O
+    H, I, Kin = 1024, 1536, 2048
+    a = O.make_case(Kin, H, M, dtype=dtype, seed=41)
+    b = O.make_case(H, 2 * I, M, dtype=dtype, seed=42)
+    lin_o = nq.WQLinear_GEMM(4, 128, Kin, H, DEV, False, dtype)
+    lin_gu = nq.WQLinear_GEMM(4, 128, H, 2 * I, DEV, False, dtype)
+    for lin, c in ((lin_o, a), (lin_gu, b)):
+        lin.qweight.copy_(c["qweight"]); lin.qscales.copy_(c["qscales"]); lin.qzeros.copy_(c["qzeros"])
+    assert lin_o.fused_supported(M, residual=True) and lin_gu.fused_supported(M, norm=True, silu_mul=True)
+    g = torch.Generator().manual_seed(5)
+    res = torch.randn(M, H, generator=g).to(dtype)
+    w = (torch.rand(H, generator=g) + 0.5).to(dtype)
+    h, ssq = lin_o.forward_fused(a["x"].to(DEV), residual=res.to(DEV))
+    y = lin_gu.forward_fused(h, norm=(ssq, w.to(DEV), 1e-6), silu_mul=True)
+    torch.cuda.synchronize()
+    tol = 2e-3 if dtype == torch.float16 else 8e-3
+    y_o = O.w4a16_ref(a["x"], a["qweight"], a["qscales"], a["qzeros"]).to(dtype)
+    h_ref = y_o + res
+    assert O.rel_err(h, h_ref) <= tol
+    hf = h_ref.float()
+    xn = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6)).to(dtype) * w
+    gu = O.w4a16_ref(xn, b["qweight"], b["qscales"], b["qzeros"]).to(dtype)
+    want = (torch.nn.functional.silu(gu[:, :I]).to(dtype) * gu[:, I:]).float()
+    assert O.rel_err(y, want) <= 2 * tol   # three 16-bit roundings (y, silu, product) on top of the GEMM's

@@ -79,9 +79,14 @@ def _run_case(K, N, M, g=128, dtype=torch.float16, seed=0, bias=False, tol=TIGHT
     m.qweight.copy_(c["qweight"]); m.qscales.copy_(c["qscales"]); m.qzeros.copy_(c["qzeros"])
     if bias:
         m.bias.copy_(c["bias"])
-    y = m(c["x"].to(DEV))
+    # The output sits between sentinel rows that no kernel may touch (a write past either end of
+    # the result would show there; compute-sanitizer is not available where these tests run).
+    SENT = -7.25
+    buf = torch.full((M + 2, N), SENT, dtype=dtype, device=DEV)
+    y = m(c["x"].to(DEV), out=buf[1:M + 1])
     torch.cuda.synchronize()
-    assert y.dtype == dtype and tuple(y.shape) == (M, N)
+    assert y.dtype == dtype and tuple(y.shape) == (M, N) and y.data_ptr() == buf[1].data_ptr()
+    assert bool((buf[0] == SENT).all()) and bool((buf[M + 1] == SENT).all()), "a kernel wrote outside its output"
     ref = O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"], c["bias"])
     err = O.rel_err(y, ref)
     bound = tol if dtype == torch.float16 else max(tol, 8e-3)  # bf16 output rounding is 2^-8 relative
@@ -208,6 +213,48 @@ def test_gemm_prefill_sizes_sampled_rows(M):
     rows = torch.randperm(M, generator=torch.Generator().manual_seed(1))[:48]
     ref = O.w4a16_ref(c["x"][rows], c["qweight"], c["qscales"], c["qzeros"])
     assert O.rel_err(y[rows.to(DEV)], ref) <= TIGHT
+
+
+# The whole benchmark sweep: every (K, N) shape at every token count the decode-shape test above does
+# not already take, against the oracle.  One seeded case per shape and dtype is built once (the oracle's
+# dense weight too) and reused for all token counts; above 40 tokens the oracle answers for a seeded
+# sample of 40 rows, which still covers every output column, every K split and every token tile position
+# modulo 128 that the sample hits.
+SWEEP_SHAPES = [(4096, 4096), (4096, 12288), (12288, 4096), (5120, 25600), (25600, 5120)]
+_sweep_cache = {}
+
+
+def _sweep_case(K, N, dtype):
+    key = (K, N, dtype)
+    if key not in _sweep_cache:
+        _sweep_cache.clear()  # one shape at a time: the dense oracle weight is up to 262 MB
+        # uniform 32-bit words are uniform nibbles: the benchmark's int4 weights and zero-points
+        # uniform in [0, 15], without the oracle packer's pass over 131 M elements
+        g = torch.Generator().manual_seed(K // 128 + N // 128)
+        c = {"qweight": torch.randint(-2 ** 31, 2 ** 31, (K, N // 8), generator=g, dtype=torch.int64).to(torch.int32),
+             "qzeros": torch.randint(-2 ** 31, 2 ** 31, (K // 128, N // 8), generator=g, dtype=torch.int64).to(torch.int32),
+             "qscales": (torch.rand(K // 128, N, generator=g) * 9e-3 + 1e-3).to(dtype),
+             "x": torch.randn(4096, K, generator=g).to(dtype)}
+        dev = {k: c[k].to(DEV) for k in ("x", "qweight", "qscales", "qzeros")}
+        _sweep_cache[key] = (c, dev, O.dequantize(c["qweight"], c["qscales"], c["qzeros"]))
+    return _sweep_cache[key]
+
+
+@pytest.mark.parametrize("M", [4, 128, 1024, 4096])
+@pytest.mark.parametrize("K,N,dtype", [(K, N, torch.float16) for K, N in SWEEP_SHAPES] +
+                         [(5120, 25600, torch.bfloat16), (25600, 5120, torch.bfloat16)])
+def test_gemm_sweep_every_point_vs_oracle(K, N, dtype, M):
+    c, dev, W = _sweep_case(K, N, dtype)
+    y = nq.awq_gemm(dev["x"][:M].contiguous(), dev["qweight"], dev["qscales"], dev["qzeros"], 8)
+    torch.cuda.synchronize()
+    assert y.dtype == dtype and tuple(y.shape) == (M, N)
+    rows = torch.arange(M) if M <= 40 else torch.randperm(M, generator=torch.Generator().manual_seed(M + K))[:40]
+    ref = c["x"][rows].float() @ W.float()
+    err = O.rel_err(y[rows.to(DEV)], ref)
+    bound = TIGHT if dtype == torch.float16 else 8e-3
+    assert err <= bound <= TOL, f"rel err {err:.3e} (K={K} N={N} M={M} {dtype})"
+    assert bool(torch.isfinite(y.float()).all())
+    _lib.check_workspaces()  # no bounded wait gave up
 
 
 def test_gemm_linearity_property_full_size():

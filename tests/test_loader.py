@@ -28,8 +28,24 @@ def checkpoint(tmp_path_factory):
     path = str(tmp_path_factory.mktemp("ckpt"))
     full = Qwen3QuantizedForCausalLM(**ARCH, device="cpu", dtype=torch.float16)
     _randomise(full, 5)
-    save_model(full, path, config={"model_type": "qwen3"}, w_bits=4, group_size=128)
+    save_model(full, path, config={"model_type": "qwen3"}, w_bits=4, group_size=128,
+               calibration={"dataset": "wikitext", "dataset_subset": "wikitext-2-raw-v1", "n_samples": 128,
+                            "max_seq_len": 512, "apply_clip": True})
     return path, full
+
+
+def test_writer_layout_matches_the_reference_writer(checkpoint):
+    # scripts/qwen3_0pt6_billion.py:188-235: model.safetensors, an index that maps every key to it, and a
+    # quantization_config block with the calibration record
+    path, full = checkpoint
+    index = json.load(open(os.path.join(path, "model.safetensors.index.json")))
+    assert index["metadata"] == {"format": "pt"}
+    assert index["weight_map"] == {k: "model.safetensors" for k in full.state_dict()}
+    quant = json.load(open(os.path.join(path, "config.json")))["quantization_config"]
+    assert list(quant) == ["quant_method", "w_bits", "group_size", "zero_point", "version", "modules_to_not_convert",
+                           "calibration"]
+    assert quant["quant_method"] == "awq" and quant["version"] == "gemm" and quant["modules_to_not_convert"] == []
+    assert list(quant["calibration"]) == ["dataset", "dataset_subset", "n_samples", "max_seq_len", "apply_clip"]
 
 
 def test_round_trip_unsharded(checkpoint):

@@ -87,3 +87,16 @@ def test_make_case_is_seeded():
     a, b = O.make_case(128, 64, 2, seed=5), O.make_case(128, 64, 2, seed=5)
     assert torch.equal(a["qweight"], b["qweight"]) and torch.equal(a["x"], b["x"])
     assert np.array_equal(O.unpack_int4(a["qweight"].numpy()), a["iw"])
+
+
+def test_threaded_dequantize_equals_the_numpy_one():
+    # the multi-threaded torch form that the benchmark's CPU baseline times
+    for (K, N, g, dtype, seed) in ((256, 136, 128, torch.float16, 1), (192, 264, 64, torch.bfloat16, 2), (1024, 3072, 128, torch.float16, 3)):
+        c = O.make_case(K, N, 1, group_size=g, dtype=dtype, seed=seed)
+        a = O.dequantize(c["qweight"], c["qscales"], c["qzeros"])
+        b = O.dequantize_threaded(c["qweight"], c["qscales"], c["qzeros"])
+        assert a.dtype == b.dtype and torch.equal(a, b)
+    words = torch.full((128, 4), -1, dtype=torch.int32)          # all-15 nibbles: the sign bit is in use
+    zeros = torch.zeros(1, 4, dtype=torch.int32)
+    s = torch.full((1, 32), 0.5, dtype=torch.float16)
+    assert torch.equal(O.dequantize_threaded(words, s, zeros), O.dequantize(words, s, zeros))
