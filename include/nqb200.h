@@ -87,7 +87,8 @@ int nqb200_gemm(const void* x, const void* qweight, const void* qscales, const v
  * 16-bit type: models/qwen3_quantized.py:150 of the reference runs them as a linear, F.silu and a
  * multiply).  The activation runs in the kernel that adds the split-K partial sums, so it costs no
  * launch of its own.  Only where nqb200_gemm_gate_up_silu_supported() says 1 (M <= 16, group 128,
- * N a multiple of 1024, K long enough that every column tile is split across CTAs); elsewhere it
+ * N a multiple of twice nqb200_decode_tile_columns(), K long enough that every column tile is split across
+ * CTAs); elsewhere it
  * returns NQB200_ERR_BAD_SHAPE and the caller runs nqb200_gemm + nqb200_silu_mul.  Workspace as
  * for nqb200_gemm with the same M, N, K. */
 int nqb200_gemm_gate_up_silu_supported(int64_t M, int64_t N, int64_t K, int64_t group_size, int dtype);
@@ -100,14 +101,17 @@ int nqb200_gemm_gate_up_silu(const void* x, const void* qweight, const void* qsc
  * nqb200_gemm_decode_fused_supported() accepts (flags = OR of NQB200_FUSE_*):
  *   RMSNORM   x is the residual stream h [M, K]; the linear's input is RMSNorm(h) * norm_weight
  *             (layers/norm.py:18-32 of the reference, same roundings), with mean(h^2) taken from sums
- *             of squares per token and 512-column tile of h: norm_ssq [M, norm_tiles], fp32.
+ *             of squares per token and column tile of h (nqb200_decode_tile_columns() columns per tile):
+ *             norm_ssq [M, norm_tiles], fp32.
  *   RESIDUAL  out [M, N] = 16-bit(16-bit(y) + residual_in) (models/qwen3_quantized.py:213-214), the
- *             new residual stream, and ssq_out [M, ceil(N/512)] = its sums of squares per token and
+ *             new residual stream, and ssq_out [M, ceil(N / nqb200_decode_tile_columns())] = its sums of squares per token and
  *             tile: what the RMSNORM prologue of the next linear reads.
  *   SILU_MUL  as nqb200_gemm_gate_up_silu (out is [M, N/2]); not together with RESIDUAL or ALLREDUCE.
  *   ALLREDUCE as nqb200_gemm_allreduce (peer_buffers != NULL); the residual is added after the sum.
  * A block then costs two launches per linear and nothing for its norms, activation and all-reduces.
  * No counterpart in the reference (its block is separate modules). */
+/* Columns per tile of the decode-sized kernels: the granularity of norm_ssq / ssq_out below. */
+int nqb200_decode_tile_columns(void);
 enum { NQB200_FUSE_RMSNORM = 1, NQB200_FUSE_RESIDUAL = 2, NQB200_FUSE_SILU_MUL = 4, NQB200_FUSE_ALLREDUCE = 8 };
 typedef struct nqb200_decode_fusion {
   const float* norm_ssq;   /* NULL: x is used as it is */

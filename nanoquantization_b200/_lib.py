@@ -35,6 +35,7 @@ SIGNATURES = {
     "nqb200_dequant": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "nqb200_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _int]),
     "nqb200_gemm": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "nqb200_decode_tile_columns": (_int, []),
     "nqb200_gemm_gate_up_silu_supported": (_int, [_i64, _i64, _i64, _i64, _int]),
     "nqb200_gemm_gate_up_silu": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "nqb200_gemm_decode_fused_supported": (_int, [_i64, _i64, _i64, _i64, _int, _int, _int, _sz]),

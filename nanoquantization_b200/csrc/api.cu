@@ -87,6 +87,8 @@ extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscal
   return launch_generic(a);
 }
 
+extern "C" int nqb200_decode_tile_columns(void) { return stream_tile_columns(); }
+
 extern "C" int nqb200_gemm_gate_up_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
   return !umma_prefill_supports(M, N, K, g) && stream_silu_supported(M, N, K, g) ? 1 : 0;

@@ -77,6 +77,7 @@ size_t umma_prefill_workspace_bytes(int64_t M, int64_t N, int64_t K);
 bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int stream_launches(int64_t M, int64_t N, int64_t K);
+int stream_tile_columns();
 bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 int umma_prefill_launches(int64_t M, int64_t N, int64_t K);

@@ -2,42 +2,31 @@
 //
 // One persistent CTA per SM.  The packed matrix is cut into units of 128 rows
 // (one quantisation group) by 512 columns; unit u = tile * G + group, so that a
-// contiguous range of units walks down K inside a column tile.  The CTA holds
-// two consumer groups of 8 warps; each group is a worker of its own with its own
-// contiguous range of units (296 workers, ranges differ by at most one unit).
-// One ring of shared-memory stages serves both: the stages are filled in the
-// order worker 0's unit, worker 1's unit, worker 0's next unit, ..., which keeps
-// the two groups in step whatever the warp scheduler prefers.
+// CTA's contiguous range of units walks down K inside a column tile.  The 148
+// CTAs take equal contiguous ranges (sizes differ by at most one unit).
 //
-//   producer warp : for each unit, four TMA tensor loads into the ring (two
-//                   128x128-byte boxes of packed weights with the 128-byte
-//                   swizzle, the group's scales and zero-points), completion on
-//                   an mbarrier.  About 165 KB per SM is in flight from the first
-//                   cycle.  It reads nothing another kernel writes, so under
+//   producer warp : for each unit, four TMA tensor loads into a shared-memory
+//                   ring (two 128x128-byte boxes of packed weights with the
+//                   128-byte swizzle, the group's scales and zero-points),
+//                   completion on an mbarrier.  About 190 KB per SM is in flight
+//                   from the first cycle, which is what keeps HBM busy at these
+//                   sizes.  It reads nothing another kernel writes, so under
 //                   programmatic stream serialisation it starts before the
 //                   kernel ahead of it has finished.
-//   activation warp : the group's 128 k of every token by plain loads, stored so
-//                   that the four k a consumer thread feeds to one mma
-//                   (2t, 2t+1, 2t+8, 2t+9 of a 16-k step) are one 8-byte word,
-//                   rows 288 bytes apart (conflict-free), and their sum per token.
-//   coefficient warp : per output column of the unit, the two fp32 factors of the
-//                   once-per-group correction, scale * 2^p and scale * zero-point,
-//                   in the order the consumer threads read them, so that four
-//                   lanes do not each convert the same scales and zero-points.
-//   2 x 8 consumer warps : warp w owns columns 64w..64w+63 of the tile for the
-//                   whole group.  One ldmatrix.x4.trans per 16-k step gives a
-//                   thread, per register, four nibbles of row k and the same four
-//                   of row k+1: the k pairs that the tensor-core operand wants,
-//                   with no byte permutes.  Two masks (and one shift) per
-//                   register make four operand registers; the raw nibbles go
-//                   into mma.sync m16n8k16 as fp16 subnormals q * 2^-24 and
-//                   q * 2^-20 (bf16: 128 + q), and scale, power of two and
-//                   zero-point are applied once per group in fp32:
-//                   y = sum_g s * (sum_k x q - z sum_k x).
+//   activation warp : the group's 128 k of every token by plain loads into the
+//                   stage (swizzled like a TMA tile), and their sum per token
+//                   (the tensor pipe is this kernel's scarce resource, so the sum
+//                   is not done with an all-ones mma).
+//   8 consumer warps : warp w owns columns 64w..64w+63 of the tile for the whole
+//                   group; arithmetic as in the register-fed kernel (raw nibbles
+//                   as fp16 subnormals into mma.sync m16n8k16, scale and
+//                   zero-point applied once per group in fp32).  The 128-byte swizzle and
+//                   the mma's own k order (2t, 2t+1, 2t+8, 2t+9) make every
+//                   shared-memory load conflict-free.
 //
-// A worker whose range covers a tile's whole K writes the output itself.  Other
-// segments go to a per-worker slot (fp32) in the workspace, and a second, small
-// kernel adds a tile's slots in worker order (so the result does not depend on
+// A CTA whose range covers a tile's whole K writes the output itself.  Other
+// segments go to a per-CTA slot (fp32) in the workspace, and a second, small
+// kernel adds a tile's slots in CTA order (so the result does not depend on
 // timing), adds the bias and writes the output.  Both kernels are launched with
 // programmatic stream serialisation: the second is resident before the first
 // ends, and the next layer's weights start to stream while it runs.
@@ -48,39 +37,35 @@
 #include "tma_utils.cuh"
 #include "peer_layout.cuh"
 #include <mutex>
-#ifndef NQ_EXP
-#define NQ_EXP 0
-#endif
 
 namespace nqb200 {
 
 constexpr int kUnitN = 512, kUnitK = 128;
-constexpr int kGroupWarps = 8, kGroups = 2;                // two workers per CTA
-constexpr int kConsumerWarps = kGroupWarps * kGroups;
-constexpr int kProducerWarp = kConsumerWarps, kXWarp = kConsumerWarps + 1, kCoefWarp = kConsumerWarps + 2;
-constexpr int kStreamThreads = (kConsumerWarps + 3) * 32;
-constexpr int kXRow = 288;                                 // bytes between the tokens' rows of a stage's activations
-constexpr int kOffW0 = 0, kOffW1 = 16384, kOffX = 32768;
+constexpr int kConsumerWarps = 8;
+constexpr int kStreamThreads = (kConsumerWarps + 2) * 32;  // consumers, TMA producer, sum(x) warp
+constexpr int kOffW0 = 0, kOffW1 = 16384, kOffX0 = 32768;
 
-// MT = 1: up to 8 tokens, MT = 2: up to 16.
+// Up to 8 tokens (MT = 1): two CTAs per SM with three stages each, so that 16 consumer warps
+// share an SM's issue slots.  Up to 16 tokens (MT = 2): one CTA per SM with five stages.
 template <int MT> struct StreamCfg {
-  static constexpr int kStages = 5;
-  static constexpr int kOffSc = kOffX + 8 * MT * kXRow;
+  static constexpr int kCtasPerSm = MT == 1 ? 2 : 1;
+  static constexpr int kStages = MT == 1 ? 3 : 5;
+  static constexpr int kXBox = 8 * MT * 128;                 // bytes of one activation box
+  static constexpr int kOffX1 = kOffX0 + kXBox;
+  static constexpr int kOffSc = kOffX0 + 2 * kXBox;
   static constexpr int kOffZ = kOffSc + 1024;
   static constexpr int kOffXs = kOffZ + 256;                  // sum over the group's k of each token, fp32
-  static constexpr int kOffCoef = kOffXs + 64;                // [warp][g][A cs0 | A cs1 | B cs0 | B cs1], 16 bytes each
-  static constexpr int kStageBytes = (kOffCoef + 4096 + 1023) / 1024 * 1024;
+  static constexpr int kStageBytes = (kOffXs + 64 + 1023) / 1024 * 1024;
   static constexpr int kSmem = kStages * kStageBytes + 1024;
   static constexpr int kSlotFloats = 8 * MT * kUnitN;         // one segment's slot
   static constexpr uint32_t kStageTx = 2 * 16384 + 1024 + 256;  // what TMA brings: weights, scales, zero-points
 };
 constexpr int kStatusWord = kCounterBytes / 4 - 1;  // last word of the counter region
-constexpr int kMaxWorkers = kNumSMs * kGroups;
 
 struct StreamParams {
   const void* bias; int bias_dtype; uint16_t* out;
   const uint16_t* x;
-  int M, N, K, G, ntiles, nctas;  // nctas: workers (consumer groups), two per CTA
+  int M, N, K, G, ntiles, nctas;
   uint32_t U;
   int* counters; float* slots;
   // Optional prologue: x is a residual stream h and the GEMM input is RMSNorm(h) * norm_weight, with
@@ -91,13 +76,16 @@ struct StreamParams {
   const uint16_t* residual_in; float* ssq_out;
 };
 
+int stream_tile_columns() { return kUnitN; }
+
 bool stream_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   return M >= 1 && M <= 16 && g == 128 && K % 128 == 0 && N % 32 == 0 && (N + kUnitN - 1) / kUnitN < kStatusWord;
 }
 
 size_t stream_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const long long U = ((N + kUnitN - 1) / kUnitN) * (K / 128);
-  const long long C = U < kMaxWorkers ? U : kMaxWorkers;
+  const long long cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
+  const long long C = U < cap ? U : cap;
   return (size_t)kCounterBytes + (size_t)C * 2 * (size_t)(M > 8 ? 16 : 8) * kUnitN * sizeof(float);
 }
 
@@ -115,95 +103,68 @@ __device__ __forceinline__ void mma16816s(float (&d)[4], uint32_t a0, uint32_t a
   }
 }
 
-// Four 8x8 matrices of 16-bit elements, transposed: lanes 8i..8i+7 give the addresses of the rows of
-// matrix i; register i of thread (g = lane / 4, t = lane % 4) holds elements [2t][g] (low half) and
-// [2t+1][g] (high half) of matrix i.
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
-}
-
 // unit ranges in 32-bit arithmetic (the host checks U * C < 2^31): 64-bit division is a long
 // dependent instruction sequence on the GPU and these run on the critical path of the tail
-__device__ __forceinline__ uint32_t cta_begin(uint32_t c, uint32_t U, uint32_t C) { return c >= C ? U : (c * U) / C; }
+__device__ __forceinline__ uint32_t cta_begin(uint32_t c, uint32_t U, uint32_t C) { return (c * U) / C; }
 __device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t U, uint32_t C) { return (int)(((u + 1) * C - 1) / U); }
 
-// The ring is filled alternately for the CTA's two workers while both have units left, then for the
-// one that has more.  Position in that order of worker `grp`'s j-th unit (n0, n1: the workers' unit counts).
-__device__ __forceinline__ int ring_index(int grp, int j, int n0, int n1) {
-  const int m = n0 < n1 ? n0 : n1;
-  return j < m ? 2 * j + grp : 2 * m + (j - m);
-}
-// ... and the inverse: worker and j of ring position idx.
-__device__ __forceinline__ void ring_owner(int idx, int n0, int n1, int& grp, int& j) {
-  const int m = n0 < n1 ? n0 : n1;
-  if (idx < 2 * m) { grp = idx & 1; j = idx >> 1; }
-  else { grp = n0 > n1 ? 0 : 1; j = m + (idx - 2 * m); }
-}
+// value of column e (0..7) of a thread's 8-column group, row t of the token pair
+#define NQ_TOTAL_AT(tot, e, t) tot[((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) >> 1][2 * (((e) & 1 ? 4 + ((e) >> 1) : ((e) >> 1)) & 1) + (t)]
 
 template <int MT, bool BF16, bool NORM>
-__global__ void __launch_bounds__(kStreamThreads, 1)
+__global__ void __launch_bounds__(kStreamThreads, StreamCfg<MT>::kCtasPerSm)
 stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
               const __grid_constant__ CUtensorMap tm_z, const StreamParams p) {
-  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u, MAGIC = 0x43004300u;
+  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
   constexpr float MULT_LO = BF16 ? 1.f : 16777216.f, MULT_HI = BF16 ? 1.f : 1048576.f, OFF = BF16 ? 128.f : 0.f;
   using Cfg = StreamCfg<MT>;
-  constexpr int kStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kOffSc = Cfg::kOffSc,
-                kOffZ = Cfg::kOffZ, kOffXs = Cfg::kOffXs, kOffCoef = Cfg::kOffCoef, kSlotFloats = Cfg::kSlotFloats;
+  constexpr int kStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kOffX1 = Cfg::kOffX1, kOffSc = Cfg::kOffSc,
+                kOffZ = Cfg::kOffZ, kOffXs = Cfg::kOffXs, kSlotFloats = Cfg::kSlotFloats;
   constexpr uint32_t kStageTx = Cfg::kStageTx;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_x[kStages], bar_coef[kStages];
+  __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_xs[kStages];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // same place, generic pointer
+  const uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));  // same place, generic pointer
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t U = p.U, C = (uint32_t)p.nctas;
+  const uint32_t u_begin = cta_begin(blockIdx.x, U, C), u_end = cta_begin(blockIdx.x + 1, U, C);
+  const int nunits = (int)(u_end - u_begin);
   const int G = p.G;
-  // the CTA's two workers
-  const uint32_t w0 = 2 * blockIdx.x, w1 = w0 + 1;
-  const uint32_t begin0 = cta_begin(w0, U, C), begin1 = cta_begin(w1, U, C), end1 = cta_begin(w1 + 1, U, C);
-  const int n0 = (int)(begin1 - begin0), n1 = (int)(end1 - begin1);
-  const int ntotal = n0 + n1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kGroupWarps);
-      mbar_init(smem_u32(&bar_x[s]), 1); mbar_init(smem_u32(&bar_coef[s]), 1);
+      mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), kConsumerWarps); mbar_init(smem_u32(&bar_xs[s]), 1);
     }
     mbar_fence_init();
   }
   __syncthreads();
 
   grid_launch_dependents();
-  if (warp != kProducerWarp && warp != kCoefWarp) grid_dependency_wait();  // these two read only weights, scales and zero-points
+  if (warp != kConsumerWarps) grid_dependency_wait();  // all but the TMA producer touch what the kernel ahead may still write
 
-  if (warp == kProducerWarp) {
+  if (warp == kConsumerWarps) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z);
+      int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
       int issued = 0;
       bool ok = true;
-      for (int i = 0; i < ntotal; ++i) {
-        int grp, j;
-        ring_owner(i, n0, n1, grp, j);
-        const uint32_t u = (grp ? begin1 : begin0) + (uint32_t)j;
-        const int tile = (int)(u / (uint32_t)G), gk = (int)(u % (uint32_t)G);
+      // Everything this thread requests (packed weights, scales, zero-points) is read-only, so it
+      // does not wait for the kernel ahead of this one on the stream; the activations come through
+      // the activation warp, which does.
+      for (int i = 0; i < nunits; ++i) {
         const int s = i % kStages;
         if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) { ok = false; break; }
         const uint32_t st = smem_base + s * kStageBytes, bar = smem_u32(&bar_full[s]);
-#ifdef NQ_GEOM
-        mbar_expect_tx(bar, 32768);
-        for (int b = 0; b < 128 / NQ_GEOM * 2; ++b)
-          tma_load_2d(st + b * (NQ_GEOM * 128), &tm_w, tile * (64 * 128 / NQ_GEOM) + 32 * b, gk * NQ_GEOM, bar);
-#else
         mbar_expect_tx(bar, kStageTx);
-        tma_load_2d(st + kOffW0, &tm_w, tile * 64, gk * kUnitK, bar);
-        tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, gk * kUnitK, bar);
-        tma_load_2d(st + kOffSc, &tm_sc, tile * 256, gk, bar);
-        tma_load_2d(st + kOffZ, &tm_z, tile * 64, gk, bar);
-#endif
+        tma_load_2d(st + kOffW0, &tm_w, tile * 64, grp * kUnitK, bar);
+        tma_load_2d(st + kOffW1, &tm_w, tile * 64 + 32, grp * kUnitK, bar);
+        tma_load_2d(st + kOffSc, &tm_sc, tile * 256, grp, bar);
+        tma_load_2d(st + kOffZ, &tm_z, tile * 64, grp, bar);
         ++issued;
+        if (++grp == G) { grp = 0; ++tile; }
       }
       if (!ok) { grid_dependency_wait(); atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT); }
       // do not leave while a copy of ours may still be landing in this CTA's shared memory
@@ -212,14 +173,15 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     }
     return;
   }
-  if (warp == kXWarp) {
+  if (warp == kConsumerWarps + 1) {
     // --------------------------------------------------------- activation warp
     // Brings the group's 128 k of every token from global memory with plain loads (they are small,
-    // L2-resident and must not queue behind the weight boxes).  Lanes 0-15 hold one token's 256 bytes
-    // (lane c: k = 8c..8c+7), lanes 16-31 the next token's.  A 16-k step's halves go to
-    // [step][t][k = 2t, 2t+1, 2t+8, 2t+9], 32 bytes per step: lane c writes its four k pairs to
-    // step c/2, t = 0..3, at byte 4 * (c % 2) of t's 8 bytes.
+    // L2-resident and must not queue behind the weight boxes), stores them in the layout of a
+    // 128-byte-swizzled tile (16-byte chunk c of row m at chunk c ^ (m & 7)), and leaves each
+    // token's sum over the group beside them.  Lanes 0-15 hold one token's 256 bytes, lanes 16-31
+    // the next token's.
     const int cc = lane & 15, half = lane >> 4;
+    int grp = (int)(u_begin % G);
     // With the RMSNorm prologue: 1 / rms of token `lane` from the per-tile sums of squares (added
     // in tile order), handed to the lanes that need it by shuffles.
     float inv_mine = 0.f;
@@ -231,27 +193,21 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
     float inv_tok[4 * MT];
 #pragma unroll
     for (int j = 0; j < 4 * MT; ++j) inv_tok[j] = __shfl_sync(0xFFFFFFFFu, inv_mine, (2 * j + half) & 31);
-    for (int i = 0; i < ntotal; ++i) {
-      int grp, jj;
-      ring_owner(i, n0, n1, grp, jj);
-      const int gk = (int)(((grp ? begin1 : begin0) + (uint32_t)jj) % (uint32_t)G);
+    for (int i = 0; i < nunits; ++i) {
       const int s = i % kStages;
       if (i >= kStages && !mbar_wait(smem_u32(&bar_empty[s]), ((i / kStages) - 1) & 1)) {
         atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
         break;
       }
-      uint8_t* st = smem_gen + s * kStageBytes;
-#if NQ_EXP == 2 || NQ_EXP == 3 || defined(NQ_GEOM)
-      if (p.M > 0) { if (lane == 0) mbar_arrive(smem_u32(&bar_x[s])); continue; }
-#endif
+      uint8_t* st = const_cast<uint8_t*>(smem_gen) + s * kStageBytes;
       uint4 v[4 * MT];
 #pragma unroll
       for (int j = 0; j < 4 * MT; ++j) {
         const int m = 2 * j + half;
-        v[j] = m < p.M ? __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + gk * kUnitK) + cc) : make_uint4(0u, 0u, 0u, 0u);
+        v[j] = m < p.M ? __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K + grp * kUnitK) + cc) : make_uint4(0u, 0u, 0u, 0u);
       }
       uint4 nw = make_uint4(0u, 0u, 0u, 0u);
-      if (NORM) nw = __ldg(reinterpret_cast<const uint4*>(p.norm_weight + gk * kUnitK) + cc);
+      if (NORM) nw = __ldg(reinterpret_cast<const uint4*>(p.norm_weight + grp * kUnitK) + cc);
 #pragma unroll
       for (int j = 0; j < 4 * MT; ++j) {
         const int m = 2 * j + half;
@@ -268,8 +224,7 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
           }
           v[j] = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        uint32_t* row = reinterpret_cast<uint32_t*>(st + kOffX + m * kXRow + (cc >> 1) * 32 + (cc & 1) * 4);
-        row[0] = v[j].x; row[2] = v[j].y; row[4] = v[j].z; row[6] = v[j].w;
+        *reinterpret_cast<uint4*>(st + ((cc >> 3) ? kOffX1 : kOffX0) + m * 128 + (((cc & 7) ^ (m & 7)) << 4)) = v[j];
         const uint32_t wds[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
         float a = 0.f;
 #pragma unroll
@@ -280,200 +235,167 @@ stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ 
         if (cc == 0) *reinterpret_cast<float*>(st + kOffXs + 4 * m) = a;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_x[s]));
-    }
-    return;
-  }
-  if (warp == kCoefWarp) {
-    // ------------------------------------------------------- coefficient warp
-    // Lane l converts words l and l + 32 of the unit's 64 packed words of zero-points (8 columns each)
-    // and their 8 scales.  Word W = 32 box + 4 chunk + wd belongs to consumer warp 4 box + chunk / 2,
-    // chunk half cs = chunk % 2; its even columns are read by the threads with g = 2 wd, its odd columns
-    // by g = 2 wd + 1, column 2 i + parity as the i-th of the thread's four.
-    for (int i = 0; i < ntotal; ++i) {
-      const int s = i % kStages;
-      if (!mbar_wait(smem_u32(&bar_full[s]), (i / kStages) & 1)) {
-        grid_dependency_wait();
-        atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
-        break;
-      }
-      uint8_t* st = smem_gen + s * kStageBytes;
-#if NQ_EXP == 2 || NQ_EXP == 4 || defined(NQ_GEOM)
-      if (p.M > 0) { if (lane == 0) mbar_arrive(smem_u32(&bar_coef[s])); continue; }
-#endif
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int Wd = lane + 32 * h;
-        const uint4 sv = lds128(st, kOffSc + (uint32_t)Wd * 16);
-        const uint32_t zw = lds32(st, kOffZ + (uint32_t)Wd * 4);
-        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-        float A[8], B[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float sc = raw16_to_float<BF16>((uint16_t)((sw[e >> 1] >> (16 * (e & 1))) & 0xFFFF));
-          const float z = (float)((zw >> (4 * (e >> 1) + 16 * (e & 1))) & 0xF);
-          A[e] = sc * (((e >> 1) & 1) ? MULT_HI : MULT_LO);
-          B[e] = sc * (z + OFF);
-        }
-        const int wcons = 4 * (Wd >> 5) + (((Wd >> 2) & 7) >> 1), cs = (Wd >> 2) & 1, wd = Wd & 3;
-        uint8_t* even = st + kOffCoef + (wcons * 8 + 2 * wd) * 64 + 16 * cs;
-        *reinterpret_cast<float4*>(even) = make_float4(A[0], A[2], A[4], A[6]);
-        *reinterpret_cast<float4*>(even + 32) = make_float4(B[0], B[2], B[4], B[6]);
-        *reinterpret_cast<float4*>(even + 64) = make_float4(A[1], A[3], A[5], A[7]);
-        *reinterpret_cast<float4*>(even + 96) = make_float4(B[1], B[3], B[5], B[7]);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_coef[s]));
+      if (lane == 0) mbar_arrive(smem_u32(&bar_xs[s]));
+      if (++grp == G) grp = 0;
     }
     return;
   }
 
   // ------------------------------------------------------------------ consumers
-  const int grp = warp >> 3, w = warp & 7;
-  const int g = lane >> 2, t = lane & 3;
-  const int nunits = grp ? n1 : n0;
-  const uint32_t u_begin = grp ? begin1 : begin0;
-  const int worker = (int)(grp ? w1 : w0);
-  // ldmatrix: lanes 8i..8i+7 address matrix i = (chunk half i / 2, k half i % 2), row lane % 8
-  const uint32_t ld_off = (uint32_t)(w >> 2) * 16384u + (uint32_t)(8 * ((lane >> 3) & 1) + (lane & 7)) * 128u +
-                          ((uint32_t)((2 * (w & 3) + (lane >> 4)) ^ (lane & 7)) << 4);
-  const uint32_t x_off = (uint32_t)kOffX + (uint32_t)g * kXRow + (uint32_t)t * 8;
-  const uint32_t coef_off = (uint32_t)kOffCoef + (uint32_t)(w * 8 + g) * 64;
+  const int gq = lane >> 2, tig = lane & 3;
+  const int w = warp;
+  const int chunk = 2 * (w & 3) + (gq >> 2), inword = (gq & 3) * 4;
+  const uint32_t w_off = (w >> 2) ? kOffW1 : kOffW0;
+  // rows 16ks + 2tig + {0,1,8,9}: (row & 7) is 2tig or 2tig+1
+  const uint32_t sw_even = ((uint32_t)(chunk ^ ((2 * tig) & 7)) << 4) + inword;
+  const uint32_t sw_odd = ((uint32_t)(chunk ^ ((2 * tig + 1) & 7)) << 4) + inword;
+  const uint32_t row0 = (uint32_t)(2 * tig) * 128;
 
   float total[MT][4][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int d = 0; d < 4; ++d)
+    for (int b = 0; b < 4; ++b)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) total[mt][d][i] = 0.f;
+      for (int i = 0; i < 4; ++i) total[mt][b][i] = 0.f;
 
-  int tile = (int)(u_begin / (uint32_t)G), gk = (int)(u_begin % (uint32_t)G);
+  int tile = (int)(u_begin / G), grp = (int)(u_begin % G);
   const int first_tile = tile;
-  int seg_begin = gk;
+  int seg_begin = grp;
+  bool alive = true;
 
-  for (int j = 0; j < nunits; ++j) {
-    const int idx = ring_index(grp, j, n0, n1);
-    const int s = idx % kStages;
-    const uint32_t par = (uint32_t)(idx / kStages) & 1u;
-    if (!mbar_wait(smem_u32(&bar_coef[s]), par) || !mbar_wait(smem_u32(&bar_full[s]), par) ||
-        !mbar_wait(smem_u32(&bar_x[s]), par)) {
+  for (int i = 0; i < nunits && alive; ++i) {
+    const int s = i % kStages;
+    if (!mbar_wait(smem_u32(&bar_full[s]), (i / kStages) & 1)) {
       atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      alive = false;
+      break;
+    }
+    if (!mbar_wait(smem_u32(&bar_xs[s]), (i / kStages) & 1)) {
+      atomicExch(p.counters + kStatusWord, NQB200_ERR_WAIT_TIMEOUT);
+      alive = false;
       break;
     }
     const uint8_t* st = smem_gen + s * kStageBytes;
-    const uint32_t st_s = smem_base + s * kStageBytes;
+    const uint8_t* wb = st + w_off + row0;
 
     float acc[MT][4][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-      for (int d = 0; d < 4; ++d)
+      for (int b = 0; b < 4; ++b)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) acc[mt][d][q] = 0.f;
+        for (int q = 0; q < 4; ++q) acc[mt][b][q] = 0.f;
+    }
 
-#if NQ_EXP == 1 || defined(NQ_GEOM)
-    if (p.M < 0)
-#endif
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      uint32_t R[4];
-      ldmatrix_x4_trans(R, st_s + ld_off + ks * 2048);
-      uint2 xb[MT];
+      const uint8_t* rb = wb + ks * 16 * 128;
+      const uint32_t w0 = lds32(rb, sw_even), w1 = lds32(rb, 128 + sw_odd);
+      const uint32_t w2 = lds32(rb, 8 * 128 + sw_even), w3 = lds32(rb, 9 * 128 + sw_odd);
+      uint32_t xb0[MT], xb1[MT];
+      const uint8_t* xbox = st + ((ks >> 2) ? kOffX1 : kOffX0);
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) xb[mt] = *reinterpret_cast<const uint2*>(st + x_off + mt * 8 * kXRow + ks * 32);
+      for (int mt = 0; mt < MT; ++mt) {
+        const uint8_t* xr = xbox + (uint32_t)(8 * mt + gq) * 128 + tig * 4;
+        xb0[mt] = lds32(xr, (uint32_t)((2 * (ks & 3)) ^ gq) << 4);
+        xb1[mt] = lds32(xr, (uint32_t)((2 * (ks & 3) + 1) ^ gq) << 4);
+      }
 #pragma unroll
-      for (int cs = 0; cs < 2; ++cs) {
-#pragma unroll
-        for (int ph = 0; ph < 2; ++ph) {
-          uint32_t a0, a1, a2, a3;
-          if (BF16) {
-            a0 = ((R[2 * cs] >> (8 * ph)) & LO) | MAGIC; a1 = ((R[2 * cs] >> (8 * ph + 4)) & LO) | MAGIC;
-            a2 = ((R[2 * cs + 1] >> (8 * ph)) & LO) | MAGIC; a3 = ((R[2 * cs + 1] >> (8 * ph + 4)) & LO) | MAGIC;
-          } else {
-            const uint32_t l = R[2 * cs] >> (8 * ph), h = R[2 * cs + 1] >> (8 * ph);
-            a0 = l & LO; a1 = l & HI; a2 = h & LO; a3 = h & HI;
-          }
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma16816s<BF16>(acc[mt][2 * cs + ph], a0, a1, a2, a3, xb[mt].x, xb[mt].y);
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t sel = (uint32_t)b | ((uint32_t)b << 4) | ((uint32_t)(4 + b) << 8) | ((uint32_t)(4 + b) << 12);
+        const uint32_t p01 = __byte_perm(w0, w1, sel), p23 = __byte_perm(w2, w3, sel);
+        uint32_t a0, a1, a2, a3;
+        if (BF16) {
+          a0 = (p01 & LO) | 0x43004300u; a1 = ((p01 >> 4) & LO) | 0x43004300u;
+          a2 = (p23 & LO) | 0x43004300u; a3 = ((p23 >> 4) & LO) | 0x43004300u;
+        } else {
+          a0 = p01 & LO; a1 = p01 & HI; a2 = p23 & LO; a3 = p23 & HI;
         }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) mma16816s<BF16>(acc[mt][b], a0, a1, a2, a3, xb0[mt], xb1[mt]);
       }
     }
 
     // scale, power of two and zero-point, once per group
     {
-      const float4 A0 = *reinterpret_cast<const float4*>(st + coef_off), A1 = *reinterpret_cast<const float4*>(st + coef_off + 16);
-      const float4 B0 = *reinterpret_cast<const float4*>(st + coef_off + 32), B1 = *reinterpret_cast<const float4*>(st + coef_off + 48);
-      const float cA[2][4] = {{A0.x, A0.y, A0.z, A0.w}, {A1.x, A1.y, A1.z, A1.w}};
-      const float cB[2][4] = {{B0.x, B0.y, B0.z, B0.w}, {B1.x, B1.y, B1.z, B1.w}};
+      float xs[MT][2];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const float2 xs = *reinterpret_cast<const float2*>(st + kOffXs + 4 * (8 * mt + 2 * t));
+        const float2 v = *reinterpret_cast<const float2*>(st + kOffXs + 4 * (8 * mt + 2 * tig));
+        xs[mt][0] = v.x; xs[mt][1] = v.y;
+      }
+      const uint4 sv = lds128(st, kOffSc + (uint32_t)(64 * w + 8 * gq) * 2);
+      const uint32_t zw = lds32(st, kOffZ + (uint32_t)(8 * w + gq) * 4);
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
-        for (int cs = 0; cs < 2; ++cs)
+      for (int j = 0; j < 8; ++j) {
+        const int b = j >> 1, r = j & 1;
+        const int e = (j < 4) ? 2 * j : 2 * (j - 4) + 1;
+        const float sc = raw16_to_float<BF16>((uint16_t)((sw[e >> 1] >> (16 * (e & 1))) & 0xFFFF));
+        const float z = (float)((zw >> (4 * j)) & 0xF);
+        const float A = sc * (r ? MULT_HI : MULT_LO), B = sc * (z + OFF);
 #pragma unroll
-          for (int ph = 0; ph < 2; ++ph)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-              const float a = cA[cs][2 * ph + r], b = cB[cs][2 * ph + r];
-              float* tt = total[mt][2 * cs + ph];
-              const float* ac = acc[mt][2 * cs + ph];
-              tt[2 * r] = fmaf(a, ac[2 * r], fmaf(-b, xs.x, tt[2 * r]));
-              tt[2 * r + 1] = fmaf(a, ac[2 * r + 1], fmaf(-b, xs.y, tt[2 * r + 1]));
-            }
+          for (int t = 0; t < 2; ++t) total[mt][b][2 * r + t] += A * acc[mt][b][2 * r + t] - B * xs[mt][t];
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
 
-    const bool tile_done = gk == G - 1;
-    if (tile_done || j == nunits - 1) {
-      // Thread (g, t) holds, per token pair and chunk half cs, columns nb + 2i + g % 2 (i = 2 ph + r) of
-      // nb = 32 (2 (w % 4) + cs) + 8 (g / 2) in its 256-column box; lane ^ 4 holds the other parity.  After
-      // one exchange the even-g lane has columns nb..nb+3 and the odd-g lane nb+4..nb+7, contiguous.
-      const bool direct = seg_begin == 0 && tile_done;  // this worker saw the tile's whole K: write the output itself
-      float* slot = p.slots + ((size_t)worker * 2 + (tile == first_tile ? 0 : 1)) * kSlotFloats;
-      const int odd = g & 1;
+    const bool tile_done = grp == G - 1;
+    if (tile_done || i == nunits - 1) {
+      const int n0 = tile * kUnitN + 64 * w + 8 * gq;
+      const bool n_ok = n0 < p.N;
+      if (seg_begin == 0 && tile_done) {
+        // this CTA saw the tile's whole K: write the output directly
+        if (n_ok) {
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+          for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int tk = 0; tk < 2; ++tk) {
-          const int m = 8 * mt + 2 * t + tk;
+            for (int t = 0; t < 2; ++t) {
+              const int m = 8 * mt + 2 * tig + t;
+              if (m < p.M) {
+                uint32_t o[4];
 #pragma unroll
-          for (int cs = 0; cs < 2; ++cs) {
-            const float v0 = total[mt][2 * cs][tk], v1 = total[mt][2 * cs][2 + tk];
-            const float v2 = total[mt][2 * cs + 1][tk], v3 = total[mt][2 * cs + 1][2 + tk];
-            const float r0 = __shfl_xor_sync(0xFFFFFFFFu, odd ? v0 : v2, 4);
-            const float r1 = __shfl_xor_sync(0xFFFFFFFFu, odd ? v1 : v3, 4);
-            float o0, o1, o2, o3;
-            if (odd) { o0 = r0; o1 = v2; o2 = r1; o3 = v3; } else { o0 = v0; o1 = r0; o2 = v1; o3 = r1; }
-            const int ncol = 256 * (w >> 2) + 32 * (2 * (w & 3) + cs) + 8 * (g >> 1) + 4 * odd;  // within the tile
-            const int n = tile * kUnitN + ncol;
-            if (m < p.M && n < p.N) {
-              if (direct) {
-                if (p.bias) {
-                  o0 += bias_to_float(p.bias, p.bias_dtype, n); o1 += bias_to_float(p.bias, p.bias_dtype, n + 1);
-                  o2 += bias_to_float(p.bias, p.bias_dtype, n + 2); o3 += bias_to_float(p.bias, p.bias_dtype, n + 3);
+                for (int e = 0; e < 8; e += 2) {
+                  float v0 = NQ_TOTAL_AT(total[mt], e, t), v1 = NQ_TOTAL_AT(total[mt], e + 1, t);
+                  if (p.bias) { v0 += bias_to_float(p.bias, p.bias_dtype, n0 + e); v1 += bias_to_float(p.bias, p.bias_dtype, n0 + e + 1); }
+                  o[e >> 1] = (uint32_t)float_to_raw16<BF16>(v0) | ((uint32_t)float_to_raw16<BF16>(v1) << 16);
                 }
-                *reinterpret_cast<uint2*>(p.out + (size_t)m * p.N + n) =
-                    make_uint2((uint32_t)float_to_raw16<BF16>(o0) | ((uint32_t)float_to_raw16<BF16>(o1) << 16),
-                               (uint32_t)float_to_raw16<BF16>(o2) | ((uint32_t)float_to_raw16<BF16>(o3) << 16));
-              } else {
-                __stcg(reinterpret_cast<float4*>(slot + m * kUnitN + ncol), make_float4(o0, o1, o2, o3));  // rows beyond M are never read
+                *reinterpret_cast<uint4*>(p.out + (size_t)m * p.N + n0) = make_uint4(o[0], o[1], o[2], o[3]);
               }
             }
-          }
         }
+      } else {
+        // rows beyond M are never read
+        float* slot = p.slots + ((size_t)blockIdx.x * 2 + (tile == first_tile ? 0 : 1)) * kSlotFloats;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int m = 8 * mt + 2 * tig + t;
+            if (m < p.M) {
+              float* dst = slot + m * kUnitN + 64 * w + 8 * gq;
+              __stcg(reinterpret_cast<float4*>(dst), make_float4(NQ_TOTAL_AT(total[mt], 0, t), NQ_TOTAL_AT(total[mt], 1, t),
+                                                                 NQ_TOTAL_AT(total[mt], 2, t), NQ_TOTAL_AT(total[mt], 3, t)));
+              __stcg(reinterpret_cast<float4*>(dst + 4), make_float4(NQ_TOTAL_AT(total[mt], 4, t), NQ_TOTAL_AT(total[mt], 5, t),
+                                                                     NQ_TOTAL_AT(total[mt], 6, t), NQ_TOTAL_AT(total[mt], 7, t)));
+            }
+          }
+      }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int d = 0; d < 4; ++d)
+        for (int b = 0; b < 4; ++b)
 #pragma unroll
-          for (int q = 0; q < 4; ++q) total[mt][d][q] = 0.f;
+          for (int q = 0; q < 4; ++q) total[mt][b][q] = 0.f;
       seg_begin = 0;
     }
-    if (++gk == G) { gk = 0; ++tile; }
+    if (++grp == G) { grp = 0; ++tile; }
   }
+
 }
 
 // Sum over the contributors j, j+W, j+2W, ... of one tile's partial segments for token m, columns
@@ -687,38 +609,43 @@ stream_reduce_allreduce_kernel(const StreamParams p, const int C, const int slot
   store_reduced<BF16>(p, tile, m, n, owner, acc, s_red);
 }
 
-// Sets the kernel's attributes on the current device (once per device) and checks that a CTA fits an SM;
-// the persistent grid (one CTA per SM) must be resident all at once.
+// CTAs of this kernel that one SM holds at a time (0 on error): the persistent grid is sized so
+// that all of it is resident at once.
 template <int MT, bool BF16>
-static bool stream_configure() {
+static int stream_ctas_per_sm() {
+  // measured once per device (the attributes set here belong to the device that is current)
   static std::mutex mu;
-  static int state[kMaxDevices] = {0};  // 0 unknown, 1 ok, -1 failed
+  static int occ[kMaxDevices];
+  static bool known[kMaxDevices] = {false};
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return false; }
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return 0; }
   std::lock_guard<std::mutex> lock(mu);
-  if (state[dev] == 0) {
+  if (!known[dev]) {
     constexpr int kStreamSmem = StreamCfg<MT>::kSmem;
-    int n = 0, n2 = 0;
-    const bool ok =
-        cudaFuncSetAttribute(stream_kernel<MT, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) == cudaSuccess &&
-        cudaFuncSetAttribute(stream_kernel<MT, BF16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess &&
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_kernel<MT, BF16, false>, kStreamThreads, kStreamSmem) == cudaSuccess &&
-        cudaFuncSetAttribute(stream_kernel<MT, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) == cudaSuccess &&
-        cudaFuncSetAttribute(stream_kernel<MT, BF16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) == cudaSuccess &&
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n2, stream_kernel<MT, BF16, true>, kStreamThreads, kStreamSmem) == cudaSuccess;
-    if (!ok) cudaGetLastError();
-    state[dev] = ok && n >= 1 && n2 >= 1 ? 1 : -1;
+    int n = 0;
+    int n2 = 0;
+    if (cudaFuncSetAttribute(stream_kernel<MT, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_kernel<MT, BF16, false>, kStreamThreads, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(stream_kernel<MT, BF16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n2, stream_kernel<MT, BF16, true>, kStreamThreads, kStreamSmem) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    if (n2 < n) n = n2;
+    occ[dev] = n < StreamCfg<MT>::kCtasPerSm ? n : StreamCfg<MT>::kCtasPerSm;
+    known[dev] = true;
   }
-  return state[dev] == 1;
+  return occ[dev];
 }
 
 template <int MT, bool BF16>
 static int launch_stream_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const StreamParams& sp,
                            int max_contributors, bool silu, const PeerEpilogue* peer, cudaStream_t st) {
-  if (!stream_configure<MT, BF16>()) return NQB200_ERR_LAUNCH;
-  const dim3 main_grid((sp.nctas + kGroups - 1) / kGroups);
-  const int rc = sp.norm_ssq ? launch_overlapped(stream_kernel<MT, BF16, true>, main_grid, dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp)
-                             : launch_overlapped(stream_kernel<MT, BF16, false>, main_grid, dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
+  // the attributes were set when the occupancy was measured
+  const int rc = sp.norm_ssq ? launch_overlapped(stream_kernel<MT, BF16, true>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp)
+                             : launch_overlapped(stream_kernel<MT, BF16, false>, dim3(sp.nctas), dim3(kStreamThreads), StreamCfg<MT>::kSmem, st, tw, ts, tz, sp);
   if (rc != NQB200_OK || max_contributors <= 1) return rc;
   const int sf = (int)StreamCfg<MT>::kSlotFloats;
   if (peer)
@@ -753,7 +680,7 @@ static int stream_max_contributors(int ntiles, int G, int C, int* fewest = nullp
 bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
   if (!stream_supports(M, N, K, g) || N % (2 * kUnitN) != 0) return false;
   const int G = (int)(K / 128), ntiles = (int)(N / kUnitN);
-  const long long U = (long long)ntiles * G, cap = (long long)kMaxWorkers;
+  const long long U = (long long)ntiles * G, cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
   int fewest = 0;
   stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap), &fewest);
   return fewest >= 2;
@@ -763,7 +690,7 @@ bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
 bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
   if (!stream_supports(M, N, K, g)) return false;
   const int G = (int)(K / 128), ntiles = (int)((N + kUnitN - 1) / kUnitN);
-  const long long U = (long long)ntiles * G, cap = (long long)kMaxWorkers;
+  const long long U = (long long)ntiles * G, cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
   int fewest = 0;
   stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap), &fewest);
   return fewest >= 2 && (long long)ntiles * M <= kEpilogueSets;
@@ -772,36 +699,28 @@ bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g) {
 // 2 when some tile needs the reducing kernel.  Assumes the full occupancy the kernel is built for.
 int stream_launches(int64_t M, int64_t N, int64_t K) {
   const int G = (int)(K / 128), ntiles = (int)((N + kUnitN - 1) / kUnitN);
-  const long long U = (long long)ntiles * G, cap = (long long)kMaxWorkers;
+  const long long U = (long long)ntiles * G, cap = (long long)kNumSMs * (M > 8 ? 1 : 2);
   return stream_max_contributors(ntiles, G, (int)(U < cap ? U : cap)) > 1 ? 2 : 1;
 }
 
 int launch_stream(const GemmArgs& a) {
-#ifdef NQ_GEOM
-  const int G = a.K / NQ_GEOM;
-  const int ntiles = (a.N + kUnitN * (128 / NQ_GEOM) - 1) / (kUnitN * (128 / NQ_GEOM));
-#else
   const int G = a.K / 128;
   const int ntiles = (a.N + kUnitN - 1) / kUnitN;
-#endif
   const long long U = (long long)ntiles * G;
-  if ((U + 1) * kMaxWorkers >= (1ll << 31)) return NQB200_ERR_TOO_LARGE;
+  if (U * 2 * kNumSMs >= (1ll << 31)) return NQB200_ERR_TOO_LARGE;
   const int mt = a.M > 8 ? 2 : 1;
   const bool bf = a.dtype == NQB200_BF16;
-  const long long cap = (long long)kMaxWorkers;
+  const int per_sm = mt == 1 ? (bf ? stream_ctas_per_sm<1, true>() : stream_ctas_per_sm<1, false>())
+                             : (bf ? stream_ctas_per_sm<2, true>() : stream_ctas_per_sm<2, false>());
+  if (per_sm <= 0) return NQB200_ERR_LAUNCH;
+  const long long cap = (long long)kNumSMs * per_sm;
   const int C = (int)(U < cap ? U : cap);
   if (!a.ws || a.ws_bytes < stream_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
   if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
   alignas(64) CUtensorMap tw, ts, tz;
-#ifdef NQ_GEOM
-  bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, NQ_GEOM, 32, CU_TENSOR_MAP_SWIZZLE_128B);
-  ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, a.K / 128, a.N / 2, 1, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
-  ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, a.K / 128, a.N / 8, 1, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
-#else
   bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
   ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, G, a.N / 2, 1, 256, CU_TENSOR_MAP_SWIZZLE_NONE);
   ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, G, a.N / 8, 1, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
-#endif
   if (!ok) return NQB200_ERR_LAUNCH;
   StreamParams sp;
   sp.bias = a.bias; sp.bias_dtype = a.bias_dtype; sp.out = (uint16_t*)a.out;
@@ -833,15 +752,16 @@ int launch_stream(const GemmArgs& a) {
 // from inside it as an error.  Such a caller cannot create the scratch buffer
 // that nqb200_gemm expects.  For them the scratch of the streaming decode kernel
 // lives in the fixed array below, which every GPU that loads this library
-// holds from load until exit (kNoAllocScratchBytes, about 18.6 MiB).
+// holds from load until exit (kNoAllocScratchBytes, about 9.4 MiB).
 //
 // The name `g_noalloc_scratch` is only a host-side handle here, not a device
 // address; the device address is fetched once per device with
 // cudaGetSymbolAddress (with that device current) and passed to the kernel.
 // ---------------------------------------------------------------------------
 namespace nqb200 {
-// counters + two slots of 16 tokens x 512 columns (fp32) for each of the 296 workers
-constexpr size_t kNoAllocScratchBytes = (size_t)kCounterBytes + (size_t)kMaxWorkers * 2 * 16 * kUnitN * sizeof(float);
+// counters + two slots for each of the 296 CTAs of the 8-token configuration (the 16-token
+// configuration needs the same: 148 CTAs with slots twice the size)
+constexpr size_t kNoAllocScratchBytes = (size_t)kCounterBytes + (size_t)2 * kNumSMs * 2 * 8 * kUnitN * sizeof(float);
 }  // namespace nqb200
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[nqb200::kNoAllocScratchBytes];

@@ -130,7 +130,8 @@ def _w4a16(x: torch.Tensor, qweight: torch.Tensor, qscales: torch.Tensor, qzeros
             f.norm_ssq, f.norm_tiles, f.norm_weight, f.norm_eps = ssq.data_ptr(), ssq.shape[1], nweight.data_ptr(), float(eps)
         if residual is not None:
             assert residual.shape == (M, N) and residual.dtype == dtype and residual.is_contiguous()
-            ssq_out = torch.empty(M, (N + 511) // 512, dtype=torch.float32, device=dev)
+            tile = lib.nqb200_decode_tile_columns()
+            ssq_out = torch.empty(M, (N + tile - 1) // tile, dtype=torch.float32, device=dev)
             f.residual_in, f.ssq_out = residual.data_ptr(), ssq_out.data_ptr()
         entry = lib.nqb200_gemm_decode_fused
         tail = (ctypes.byref(f),) + (tuple(peer) if peer is not None else (None, 0, 0, 0, 0)) + tail

@@ -181,7 +181,8 @@ def test_linears_with_norm_prologue_and_residual_epilogue(M, dtype):
     assert lin_o.fused_supported(M, residual=True) and lin_q.fused_supported(M, norm=True)
     h, ssq = lin_o.forward_fused(x, residual=res)
     assert torch.equal(h, lin_o(x) + res)
-    assert ssq.shape == (M, H // 512)
+    from nanoquantization_b200 import _lib
+    assert ssq.shape == (M, H // _lib.load().nqb200_decode_tile_columns())
     want_ss = (h.float() ** 2).sum(1)
     assert float((ssq.sum(1) - want_ss).abs().max()) <= 1e-5 * float(want_ss.max())
     got = lin_q.forward_fused(h, norm=(ssq, w, 1e-6))
