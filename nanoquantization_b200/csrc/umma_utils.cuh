@@ -86,12 +86,6 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// One arrival on the barrier at this shared-memory offset in every CTA of `mask` (bit r: CTA r of the pair)
-// when every MMA issued so far by this thread has completed.  `bar` is the executing CTA's own address.
-__device__ __forceinline__ void umma_commit_pair_multicast(uint32_t bar, uint16_t mask) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"(mask) : "memory");
-}
 // The MMAs with the 64-bit shared-memory descriptor given as its two halves (the high half is constant for
 // a kernel, the low half is a base plus an offset: one 32-bit add per MMA for the issuing thread).
 __device__ __forceinline__ void umma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t desc_lo, uint32_t desc_hi, uint32_t idesc,
