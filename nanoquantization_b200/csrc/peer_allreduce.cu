@@ -24,7 +24,7 @@
 
 namespace nqb200 {
 
-constexpr int kArThreads = 256;
+constexpr int kArThreads = 256, kArThreadsLarge = 1024;  // per CTA; the larger for messages of 128 KB and more
 
 struct ArParams {
   uint8_t* peers[kMaxRanks];   // every rank's comm buffer as mapped into this process (peers[rank] is our own)
@@ -43,7 +43,7 @@ __device__ __forceinline__ uint4 ld_peer(const uint4* p) {
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const ArParams p) {
+__global__ void __launch_bounds__(kArThreadsLarge) peer_allreduce_kernel(const ArParams p) {
   grid_launch_dependents();
   grid_dependency_wait();  // our slot was filled by the kernel ahead on the stream
   uint8_t* mine = p.peers[p.rank];
@@ -74,15 +74,21 @@ __global__ void __launch_bounds__(kArThreads) peer_allreduce_kernel(const ArPara
   if (!s_ok) return;
   const int64_t nvec = p.n >> 3;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-    for (int r = 0; r < p.world; ++r) {
-      const uint4 v = ld_peer(reinterpret_cast<const uint4*>(p.peers[r] + kArOffData + p.slot_off) + i);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // every rank's 16 bytes are requested before any is used: one NVLink round trip per iteration, not one per rank
+    uint4 v[kMaxRanks];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[2 * j] += raw16_to_float<BF16>((uint16_t)(w[j] & 0xFFFF));
-        acc[2 * j + 1] += raw16_to_float<BF16>((uint16_t)(w[j] >> 16));
+    for (int r = 0; r < kMaxRanks; ++r)
+      v[r] = r < p.world ? ld_peer(reinterpret_cast<const uint4*>(p.peers[r] + kArOffData + p.slot_off) + i) : make_uint4(0u, 0u, 0u, 0u);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < p.world) {  // in rank order: the same bits on every rank
+        const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += raw16_to_float<BF16>((uint16_t)(w[j] & 0xFFFF));
+          acc[2 * j + 1] += raw16_to_float<BF16>((uint16_t)(w[j] >> 16));
+        }
       }
     }
     if (p.bias) {
@@ -164,6 +170,7 @@ extern "C" int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int wo
   p.n = M * N; p.N = (int)N;
   cudaStream_t st = (cudaStream_t)stream;
   // always the same number of CTAs: each CTA has its own flags and call counter
+  const int threads = M * N * 2 >= (128 << 10) ? kArThreadsLarge : kArThreads;
   return launch_overlapped(dtype == NQB200_BF16 ? peer_allreduce_kernel<true> : peer_allreduce_kernel<false>, dim3(kArBlocks),
-                           dim3(kArThreads), 0, st, p);
+                           dim3(threads), 0, st, p);
 }
