@@ -43,6 +43,7 @@ static int check_shape(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
 
 extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
+  if (umma_pair_supports(M, N, K, g)) return umma_pair_workspace_bytes(M, N, K);
   if (umma_prefill_supports(M, N, K, g)) return umma_prefill_workspace_bytes(M, N, K);
   if (stream_supports(M, N, K, g)) return stream_workspace_bytes(M, N, K);
   if (!decode_mma_supports(M, N, K, g)) return 0;
@@ -52,6 +53,7 @@ extern "C" size_t nqb200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, i
 
 extern "C" const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK) return "invalid";
+  if (umma_pair_supports(M, N, K, g)) return "prefill_tcgen05_pair";
   if (umma_prefill_supports(M, N, K, g)) return "prefill_tcgen05";
   if (stream_supports(M, N, K, g)) return "decode_stream";
   if (!decode_mma_supports(M, N, K, g)) return "generic";
@@ -60,6 +62,7 @@ extern "C" const char* nqb200_gemm_kernel_name(int64_t M, int64_t N, int64_t K, 
 
 extern "C" int nqb200_gemm_launch_count(int64_t M, int64_t N, int64_t K, int64_t g, int dtype) {
   if (check_shape(M, N, K, g, dtype) != NQB200_OK || M == 0) return 0;
+  if (umma_pair_supports(M, N, K, g)) return umma_pair_launches(M, N, K);
   if (umma_prefill_supports(M, N, K, g)) return umma_prefill_launches(M, N, K);
   if (stream_supports(M, N, K, g)) return stream_launches(M, N, K);
   return 1;
@@ -81,6 +84,7 @@ extern "C" int nqb200_gemm(const void* x, const void* qweight, const void* qscal
   a.bias = bias; a.bias_dtype = bias_dtype; a.out = out;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.g = (int)g; a.dtype = dtype;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = (cudaStream_t)stream;
+  if (umma_pair_supports(M, N, K, g)) return launch_umma_pair(a);
   if (umma_prefill_supports(M, N, K, g)) return launch_umma_prefill(a);
   if (stream_supports(M, N, K, g)) return launch_stream(a);
   if (decode_mma_supports(M, N, K, g)) return launch_decode_mma(a);

@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 LIB_DIR = os.path.join(os.path.dirname(HERE), "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libnqb200.so")
-SOURCES = ["api.cu", "unpack_dequant.cu", "gemm_decode.cu", "gemm_stream.cu", "gemm_umma_prefill.cu", "quantize_pack.cu", "fused_elementwise.cu", "peer_allreduce.cu"]
+SOURCES = ["api.cu", "unpack_dequant.cu", "gemm_decode.cu", "gemm_stream.cu", "gemm_umma_prefill.cu", "gemm_umma_pair.cu", "quantize_pack.cu", "fused_elementwise.cu", "peer_allreduce.cu"]
 HEADERS = ["common.cuh", "tma_utils.cuh", "umma_utils.cuh", os.path.join(ROOT, "include", "nqb200.h")]
 
 

@@ -81,6 +81,11 @@ int stream_tile_columns();
 bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 int umma_prefill_launches(int64_t M, int64_t N, int64_t K);
+// gemm_umma_pair.cu: the two-SM (cta_group::2) tcgen05 kernel for more than 128 tokens.
+int launch_umma_pair(const GemmArgs& a);
+bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g);
+size_t umma_pair_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int umma_pair_launches(int64_t M, int64_t N, int64_t K);
 bool decode_mma_supports(int64_t M, int64_t N, int64_t K, int64_t g);
 
 // ---- device helpers -------------------------------------------------------

@@ -1,0 +1,658 @@
+// Prefill kernel on the 5th-generation tensor cores: W4A16 GEMM for more than
+// 16 tokens, group size 128.
+//
+//   D[n, tok] (TMEM, fp32) = sum_k W[k, n] (TMEM, 16-bit) * x[tok, k] (smem)
+//
+// The weights are the 128-row A operand, dequantised to their true 16-bit
+// values (q - z) * s -- the integer difference first, then one multiply, which
+// is the reference's rounding -- straight from registers into tensor memory;
+// the tokens are the N dimension of the MMA, read from shared memory as a
+// K-major operand that TMA wrote with the 128-byte swizzle.  A packed word
+// never touches shared memory again after the TMA load, and a dequantised
+// value never touches shared memory at all.
+//
+// What bounds this kernel is the dequantisation (about 15 ALU instructions per
+// packed word), so a dequantised weight must feed as many tokens as possible:
+// a CTA owns 128 weight columns (one A block: 64 columns of tensor memory per
+// 128-k slot, four slots, one per stage of the activation ring) and accumulates up to 256 tokens at once (D: 256
+// columns of tensor memory).  Above 128 tokens two CTAs of a cluster (the two
+// SMs of a TPC) work as one: tcgen05.mma.cta_group::2 with M = 256 (128 weight
+// columns from each CTA's tensor memory) and N = up to 256 tokens, of which each
+// CTA loads only its half of the activation tile.  Per CTA and 128-k group that
+// is 8 KB of packed weights and at most 32 KB of activations for 1024 cycles of
+// tensor-core work.  Up to 128 tokens a CTA works alone (cta_group::1, N =
+// tokens rounded up to 16).
+//
+// Work is dealt as stream-K: a unit is one 128-k group of one output tile
+// (128 x CTAs weight columns by NT tokens); cluster c takes the contiguous
+// range [c U / C, (c + 1) U / C) of units, token tiles fastest so that
+// neighbours share packed weights in L2.  A segment that covers a tile's whole
+// K is written to the output by the epilogue; other segments go to fp32 slots
+// (two per cluster) and a second kernel adds a tile's segments in cluster order
+// (results do not depend on timing), adds the bias and writes the output.
+//
+//   warps 0, 30   TMA producers: two boxes of activations (128-byte swizzle) per unit
+//                 into a ring of four stages; 128 x 64 B of packed weights (64-byte
+//                 swizzle) with the group's scales and zero-points into a ring of
+//                 eight, freed by the dequantisers, so weights are fetched far ahead.
+//   warp 1        MMA issuer (the leader CTA's, for a pair): per k-step one
+//                 tcgen05.mma (M = 128 or 256, N = tokens, K = 16), accumulating
+//                 over the segment's K in tensor memory.
+//   warps 2-17    dequantisers, two sets of 8 taking alternate units.  Warp
+//                 (lane quarter q, k half h) takes the 32 columns of chunk q for
+//                 k-steps 4h..4h+3: ldmatrix.x2.trans gives a thread four nibbles
+//                 of row k and of row k+1 per register (the k pairs of the
+//                 operand layout); masks make 1024+q (1024+16q for the odd
+//                 nibbles, 128+q in bf16), a subtract (or fma by 1/16) removes
+//                 offset and zero-point exactly, a multiply applies the scale;
+//                 tcgen05.st.16x128b.x2 puts them into 16 lanes of the A slot.
+//   warps 18-29   epilogue at the end of a segment: D -> registers -> out[tok, n]
+//                 (+ bias, 16-bit) or the fp32 slot.
+//
+// Every wait is bounded; on expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in
+// the workspace status word, all roles drain, both CTAs of a pair meet at the
+// closing cluster barrier, and tensor memory is released.
+#include "common.cuh"
+#include "tma_utils.cuh"
+#include "umma_utils.cuh"
+#include <mutex>
+
+#ifdef NQ_TL
+static unsigned long long* g_tl_host = nullptr;
+extern "C" int nqb200_debug_set_timeline(unsigned long long* p) { g_tl_host = p; return 0; }
+#endif
+namespace nqb200 {
+// One arrival on the barrier at this shared-memory offset in every CTA of `mask` (bit r: CTA r of the pair) when
+// every MMA issued so far by this thread has completed.  `bar` is the executing CTA's own address.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask) : "memory");
+}
+namespace pair {
+
+constexpr int kCols = 128, kUnitK = 128;
+// Two rings of shared memory and one of tensor memory.  The packed weights of a unit (with scales and
+// zero-points: 8.5 KB) are done with as soon as the dequantisers have read them, so they get a deep ring of
+// their own and are fetched far ahead.  The unit's activations (up to 32 KB) must stay until its MMAs have
+// completed, exactly as long as its slot of the A operand in tensor memory: those two rings have the same depth
+// and one completion report frees both.  A unit's data is therefore requested while four units of tensor-core
+// work are still queued, and the fetch of the weights, their dequantisation and the fetch of the activations
+// overlap instead of following one another.
+constexpr int kXStages = 4, kWStages = 3;
+// A parity wait is only right if the waiter has seen the phase before: the two sets of dequantisers take
+// alternate units, so with an odd number of weight stages a stage alternates between the sets.  The "landed"
+// barriers are therefore counted per unit modulo twice the ring: each is then always waited on by the same set,
+// phase after phase.
+constexpr int kWBars = 2 * kWStages;
+constexpr int kDequantWarps = 16, kEpiWarps = 12;
+constexpr int kWProducerWarp = 2 + kDequantWarps + kEpiWarps;
+constexpr int kThreads = (kWProducerWarp + 1) * 32;
+constexpr int kXStageBytes = 32768, kWStageBytes = 8704, kOffSc = 8192, kOffZ = kOffSc + 256;
+constexpr int kOffWRing = kXStages * kXStageBytes;
+constexpr int kOffOut = kOffWRing + kWStages * kWStageBytes;   // the 16-bit output tile, [token][128 columns]
+constexpr int kOutBytes = 256 * kCols * 2;
+constexpr int kSmem = kOffOut + kOutBytes + 1024;
+constexpr uint32_t kWStageTx = 8192 + 256 + 64;
+constexpr int kColA = 0, kColD = 256, kTmemCols = 512;
+constexpr int kFixThreads = 256;
+constexpr int kFixupUnits = 55;   // measured: 30 to 60 us, a unit being about 1 us
+
+struct Params {
+  const void* bias; int bias_dtype; uint16_t* out;
+  int M, N, G;
+  int ntn, ntt;        // output tiles: column tiles of 128 x CTAs, token tiles of NT
+  int NT, TH;          // tokens per tile (the MMA's N) and per CTA (NT / CTAs)
+  int nclusters, quantum;   // quantum: 1 (stream-K) or G (a cluster takes whole tiles)
+  uint32_t U;          // units: ntn * ntt * G
+  float* slots; int slot_floats;  // [2 * nclusters][CTAs * 128][NT] fp32
+  int* status;         // may be null
+#ifdef NQ_TL
+  unsigned long long* tl;
+#endif
+};
+
+// `sleep_ns` > 0: back off between polls (roles that wait long should not take issue slots).
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                         unsigned sleep_ns = 0) {
+  const uint32_t b = smem_u32(bar);
+  if (mbar_try_wait(b, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(b, parity)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if ((i & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicExch(status, NQB200_ERR_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+template <bool BF16> __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (BF16) asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (BF16) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t fma2_f16(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+
+// cluster c's units: [range_begin(c), range_begin(c + 1)), boundaries on multiples of q units (q = 1: stream-K;
+// q = a tile's units: whole tiles only); 32-bit arithmetic (the host checks U * C < 2^31)
+__host__ __device__ __forceinline__ uint32_t range_begin(uint32_t c, uint32_t U, uint32_t C, uint32_t q) {
+  return c >= C ? U : ((c * (U / q)) / C) * q;
+}
+__host__ __device__ __forceinline__ int cluster_of_unit(uint32_t u, uint32_t U, uint32_t C) { return (int)(((u + 1) * C - 1) / U); }
+
+// The column of the CTA's 128 that lane `l` of tensor memory holds (the order the dequantisers' stores give).
+__device__ __forceinline__ int column_of_lane(int l) {
+  const int q = l >> 5, ph = (l >> 4) & 1, r = (l >> 3) & 1, g = l & 7;
+  return 32 * q + 8 * (g >> 1) + 4 * ph + 2 * r + (g & 1);
+}
+
+template <bool BF16, int CTAS>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
+                    const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x,
+                    const __grid_constant__ CUtensorMap tm_out, const Params p) {
+  constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
+  constexpr uint32_t MAGIC = BF16 ? 0x43004300u : 0x64006400u;  // 128.0 / 1024.0 in both halves
+  constexpr uint32_t SIXTEENTH = 0x2C002C00u;                   // 1/16 in both halves (fp16)
+
+  extern __shared__ uint8_t smem_raw[];
+  // wfull / wfree: the weight ring (TMA landed / the set's 8 dequantiser warps have read it).
+  // xfull: the activations landed.  afull: the A slot is filled and the CTA's activations have landed (of a
+  // pair only the leader's is waited on: it collects both CTAs' arrivals, like "D empty").  done: the unit's
+  // MMAs have completed: its activation stage and its A slot are free.
+  __shared__ __align__(8) uint64_t bar_wfull[kWBars], bar_wfree[kWStages], bar_xfull[kXStages], bar_afull[kXStages],
+      bar_done[kXStages], bar_dfull, bar_dempty, bar_drain, bar_ofull, bar_ofree;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort_i;
+
+  volatile int* s_abort = &s_abort_i;
+  int* status = p.status;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;
+  const uint32_t cluster_id = blockIdx.x / CTAS;
+  const int G = p.G;
+  const uint32_t u_begin = range_begin(cluster_id, p.U, (uint32_t)p.nclusters, (uint32_t)p.quantum);
+  const uint32_t u_end = range_begin(cluster_id + 1, p.U, (uint32_t)p.nclusters, (uint32_t)p.quantum);
+  const int nunits = (int)(u_end - u_begin);
+
+  grid_launch_dependents();
+  grid_dependency_wait();  // the activations come from the kernel ahead on the stream
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kWBars; ++s) mbar_init(smem_u32(&bar_wfull[s]), 1);
+    for (int s = 0; s < kWStages; ++s) mbar_init(smem_u32(&bar_wfree[s]), kDequantWarps / 2);
+    for (int s = 0; s < kXStages; ++s) {
+      mbar_init(smem_u32(&bar_xfull[s]), 1); mbar_init(smem_u32(&bar_afull[s]), CTAS * kDequantWarps / 2); mbar_init(smem_u32(&bar_done[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_dfull), 1);
+    mbar_init(smem_u32(&bar_dempty), CTAS * kEpiWarps);
+    mbar_init(smem_u32(&bar_drain), 1);
+    mbar_init(smem_u32(&bar_ofull), kEpiWarps);
+    mbar_init(smem_u32(&bar_ofree), 1);
+    s_abort_i = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    if (CTAS == 2) { tmem_alloc_pair(smem_u32(&s_tmem), kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(smem_u32(&s_tmem), kTmemCols); tmem_relinquish(); }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them from the other side
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  if (warp == 0) {
+    // ------------------------------------------------- producer of the activations
+    if (lane == 0) {
+      prefetch_tmap(&tm_x);
+      const uint32_t tx_bytes = 2u * (uint32_t)p.TH * 128u;
+      int issued = 0;
+      for (int i = 0; i < nunits; ++i) {
+        const uint32_t u = u_begin + (uint32_t)i;
+        const int item = (int)(u / (uint32_t)G), gk = (int)(u % (uint32_t)G);
+        const int tok_row = (item % p.ntt) * p.NT + (int)rank * p.TH;   // this CTA's part of the token tile
+        const int s = i % kXStages;
+        if (i >= kXStages && !wait_bar(&bar_done[s], ((i / kXStages) - 1) & 1, s_abort, status)) break;
+#ifdef NQ_TL
+        if (p.tl && blockIdx.x == 0 && i < 512) p.tl[i] = global_timer_ns();   // unit i - 4 has completed
+#endif
+        const uint32_t st = smem_base + s * kXStageBytes, bar = smem_u32(&bar_xfull[s]);
+        mbar_expect_tx(bar, tx_bytes);
+        tma_load_2d(st, &tm_x, gk * kUnitK, tok_row, bar);
+        tma_load_2d(st + p.TH * 128, &tm_x, gk * kUnitK + 64, tok_row, bar);
+        ++issued;
+      }
+      // do not leave while a copy of ours may still be landing in this CTA's shared memory
+      for (int j = issued > kXStages ? issued - kXStages : 0; j < issued; ++j)
+        mbar_wait(smem_u32(&bar_xfull[j % kXStages]), (j / kXStages) & 1);
+    }
+  } else if (warp == kWProducerWarp) {
+    // ----------------------------------- producer of the packed weights, scales and zero-points
+    if (lane == 0) {
+      prefetch_tmap(&tm_w); prefetch_tmap(&tm_sc); prefetch_tmap(&tm_z);
+      int issued = 0;
+      for (int i = 0; i < nunits; ++i) {
+        const uint32_t u = u_begin + (uint32_t)i;
+        const int item = (int)(u / (uint32_t)G), gk = (int)(u % (uint32_t)G);
+        const int col_tile = (item / p.ntt) * CTAS + (int)rank;          // this CTA's 128 columns
+        const int s = i % kWStages;
+        if (i >= kWStages && !wait_bar(&bar_wfree[s], ((i / kWStages) - 1) & 1, s_abort, status)) break;
+        const uint32_t st = smem_base + kOffWRing + s * kWStageBytes, bar = smem_u32(&bar_wfull[i % kWBars]);
+        mbar_expect_tx(bar, kWStageTx);
+        tma_load_2d(st, &tm_w, col_tile * 16, gk * kUnitK, bar);
+        tma_load_2d(st + kOffSc, &tm_sc, col_tile * 64, gk, bar);
+        tma_load_2d(st + kOffZ, &tm_z, col_tile * 16, gk, bar);
+        ++issued;
+      }
+      for (int j = issued > kWStages ? issued - kWStages : 0; j < issued; ++j)
+        mbar_wait(smem_u32(&bar_wfull[j % kWBars]), (j / kWBars) & 1);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (of a pair: the leader's)
+    // One thread, so every instruction here is on the critical path at several cycles each: counters instead
+    // of divisions, the descriptor as a base plus precomputed offsets, one completion report per unit.
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(BF16 ? 1 : 0, 128 * CTAS, p.NT);
+      const uint64_t desc0 = umma_smem_desc_sw128(smem_base);
+      const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
+      const uint32_t x1 = ((uint32_t)p.TH * 128u) >> 4;          // second activation box, in the descriptor's 16-byte units
+      uint32_t s = 0, phase = 0;
+      int gk = (int)(u_begin % (uint32_t)G), li = 0;
+      bool first = true;
+      for (uint32_t u = u_begin; u < u_end; ++u) {
+        const bool last = gk == G - 1 || u == u_end - 1;
+        if (first && li > 0 && !wait_bar(&bar_dempty, (li - 1) & 1, s_abort, status)) break;   // the epilogues drained D
+        if (!wait_bar(&bar_xfull[s], phase, s_abort, status)) break;
+        if (!wait_bar(&bar_afull[s], phase, s_abort, status)) break;   // (both CTAs') A slot filled, activations landed
+        tc_fence_after();
+        const uint32_t lo = desc_lo0 + s * (uint32_t)(kXStageBytes >> 4);
+        const uint32_t a = tmem + kColA + s * 64, d = tmem + kColD;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t dlo = lo + (ks >> 2) * x1 + (ks & 3) * 2;
+          const uint32_t acc = ks > 0 ? 1u : (first ? 0u : 1u);
+          if (CTAS == 2) umma_ts_pair_lohi(d, a + ks * 8, dlo, desc_hi, idesc, acc);
+          else umma_ts_lohi(d, a + ks * 8, dlo, desc_hi, idesc, acc);
+        }
+        if (CTAS == 2) {
+          umma_commit_pair_both(smem_u32(&bar_done[s]), 3);
+          if (last) umma_commit_pair_both(smem_u32(&bar_dfull), 3);
+        } else {
+          umma_commit(smem_u32(&bar_done[s]));
+          if (last) umma_commit(smem_u32(&bar_dfull));
+        }
+        if (last) ++li;
+        first = last;
+        if (++gk == G) gk = 0;
+        if (++s == kXStages) { s = 0; phase ^= 1u; }
+      }
+      // everything issued has completed before tensor memory may be released
+      if (CTAS == 2) umma_commit_pair(map_to_cta(smem_u32(&bar_drain), 0)); else umma_commit(smem_u32(&bar_drain));
+      mbar_wait(smem_u32(&bar_drain), 0);
+    }
+  } else if (warp < 2 + kDequantWarps) {
+    // -------------------------------------------------------------- dequantisers
+    const int dw = warp - 2;
+    const int q = warp & 3, h = (dw >> 2) & 1, set = dw >> 3;  // set: which units (even / odd) this warp serves
+    const int g = lane >> 2, odd = g & 1;
+    const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
+    const uint32_t afull_addr = CTAS == 2 ? map_to_cta(smem_u32(&bar_afull[0]), 0) : smem_u32(&bar_afull[0]);
+    // ldmatrix: lanes 0-7 address rows k = 0..7 of a k-step, lanes 8-15 rows 8..15 (the others repeat them);
+    // rows are 64 bytes, 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
+    const int lr = lane & 15;
+    const uint32_t ld_row = (uint32_t)lr * 64u, ld_x = (uint32_t)((lr >> 1) & 3);
+    for (int i = set; i < nunits; i += 2) {
+      const int sw = i % kWStages, sa = i % kXStages;
+      if (!wait_bar(&bar_wfull[i % kWBars], (i / kWBars) & 1, s_abort, status)) break;
+      const uint32_t st = smem_base + kOffWRing + sw * kWStageBytes;
+      // per column of this thread's four (2 pp + odd of word 4q + g/2): the scale, and what to remove, in both halves
+      uint32_t sc2[4], zm2[4];
+      {
+        uint32_t swd[4], zw;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(swd[0]), "=r"(swd[1]), "=r"(swd[2]), "=r"(swd[3])
+                     : "r"(st + kOffSc + (uint32_t)(4 * q + (g >> 1)) * 16u));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw) : "r"(st + kOffZ + (uint32_t)(4 * q + (g >> 1)) * 4u));
+#pragma unroll
+        for (int pp = 0; pp < 4; ++pp) {
+          sc2[pp] = odd ? __byte_perm(swd[pp], 0, 0x3232) : __byte_perm(swd[pp], 0, 0x1010);
+          const uint32_t z = (zw >> (4 * pp + 16 * odd)) & 0xFu;
+          if (!BF16 && (pp & 1)) {
+            // odd nibbles arrive as 1024 + 16 q: fma by 1/16 with -(64 + z) gives q - z exactly.
+            // -(64 + z) in fp16: 0xD400 is -64, and integers 64..79 are steps of 1/16 of its binade: low mantissa bits z << 4
+            const uint32_t hneg = 0xD400u | (z << 4);
+            zm2[pp] = hneg | (hneg << 16);
+          } else {
+            zm2[pp] = (z | (z << 16)) | MAGIC;  // 1024 + z (128 + z): integers in the magic's binade are its low mantissa bits
+          }
+        }
+      }
+      // the A slot is free once the MMAs of the unit four before this one have completed
+      if (i >= kXStages && !wait_bar(&bar_done[sa], ((i / kXStages) - 1) & 1, s_abort, status)) break;
+      tc_fence_after();
+      const uint32_t acol = lane_base + kColA + sa * 64;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const int ks = 4 * h + kk;
+        uint32_t R0, R1;
+        // ((16 ks + lr) >> 1) & 3 == (lr >> 1) & 3
+        ldmatrix_x2_trans(R0, R1, st + (uint32_t)ks * 1024u + ld_row + (((uint32_t)q ^ ld_x) << 4));
+#pragma unroll
+        for (int ph = 0; ph < 2; ++ph) {
+          uint32_t a0, a1, a2, a3;
+          if (BF16) {
+            a0 = ((R0 >> (8 * ph)) & LO) | MAGIC; a1 = ((R0 >> (8 * ph + 4)) & LO) | MAGIC;
+            a2 = ((R1 >> (8 * ph)) & LO) | MAGIC; a3 = ((R1 >> (8 * ph + 4)) & LO) | MAGIC;
+            a0 = mul2<true>(sub2<true>(a0, zm2[2 * ph]), sc2[2 * ph]);
+            a2 = mul2<true>(sub2<true>(a2, zm2[2 * ph]), sc2[2 * ph]);
+            a1 = mul2<true>(sub2<true>(a1, zm2[2 * ph + 1]), sc2[2 * ph + 1]);
+            a3 = mul2<true>(sub2<true>(a3, zm2[2 * ph + 1]), sc2[2 * ph + 1]);
+          } else {
+            const uint32_t l = R0 >> (8 * ph), hh = R1 >> (8 * ph);
+            a0 = (l & LO) | MAGIC; a1 = (l & HI) | MAGIC; a2 = (hh & LO) | MAGIC; a3 = (hh & HI) | MAGIC;
+            a0 = mul2<false>(sub2<false>(a0, zm2[2 * ph]), sc2[2 * ph]);
+            a2 = mul2<false>(sub2<false>(a2, zm2[2 * ph]), sc2[2 * ph]);
+            a1 = mul2<false>(fma2_f16(a1, SIXTEENTH, zm2[2 * ph + 1]), sc2[2 * ph + 1]);
+            a3 = mul2<false>(fma2_f16(a3, SIXTEENTH, zm2[2 * ph + 1]), sc2[2 * ph + 1]);
+          }
+          tmem_st_16x128b_x2(acol + ((uint32_t)(16 * ph) << 16) + 8 * ks, a0, a1, a2, a3);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_wfree[sw]));   // this warp has read what it needs of the packed tile
+      tc_wait_st();
+      tc_fence_before();
+      // this CTA's half of the activations must have landed too before the (leader's) issuer may go
+      if (!wait_bar(&bar_xfull[sa], (i / kXStages) & 1, s_abort, status)) break;
+      __syncwarp();
+      if (lane == 0) {
+        if (CTAS == 2) mbar_arrive_cluster(afull_addr + (uint32_t)sa * 8u);  // the leader's barrier, from either CTA
+        else mbar_arrive(afull_addr + (uint32_t)sa * 8u);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3, sub = (warp - 2 - kDequantWarps) >> 2;
+    const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
+    const int n_local = column_of_lane(32 * q + lane);
+    const uint32_t dempty_addr = CTAS == 2 ? map_to_cta(smem_u32(&bar_dempty), 0) : smem_u32(&bar_dempty);
+    int li = 0, ow = 0;                    // tiles read from D; tiles that went out through the staging area
+    const int first_item = (int)(u_begin / (uint32_t)G);
+    uint32_t u = u_begin;
+    while (u < u_end) {
+      // the segment of this item that the cluster covers: groups [g0, g1)
+      const int item = (int)(u / (uint32_t)G), g0 = (int)(u % (uint32_t)G);
+      const uint32_t item_end = (uint32_t)(item + 1) * (uint32_t)G;
+      const uint32_t seg_end = item_end < u_end ? item_end : u_end;
+      const int g1 = g0 + (int)(seg_end - u);
+      u = seg_end;
+      const int tn = item / p.ntt, tt = item % p.ntt;
+      if (!wait_bar(&bar_dfull, li & 1, s_abort, status, 200)) break;
+      tc_fence_after();
+      const bool whole = g0 == 0 && g1 == G;
+      const int n = (tn * CTAS + (int)rank) * kCols + n_local;
+      const bool n_ok = n < p.N;
+      const int tok0 = tt * p.NT;
+      float* slot = p.slots + ((size_t)cluster_id * 2 + (item == first_item ? 0 : 1)) * p.slot_floats +
+                    (size_t)((int)rank * kCols + n_local) * p.NT;
+      const float bv = (whole && p.bias && n_ok) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
+      if (whole) {
+        // The tile leaves through shared memory: [token][column] in 16 bits, written by one TMA store that clips
+        // at M and N.  The accumulator is handed back as soon as it has been read.
+        if (ow > 0 && !wait_bar(&bar_ofree, (ow - 1) & 1, s_abort, status)) break;   // the previous store has read the staging area
+        uint8_t* stage = smem_raw + (smem_base - smem_u32(smem_raw)) + kOffOut + n_local * 2;
+        for (int c0 = 16 * sub; c0 < p.NT; c0 += 16 * (kEpiWarps / 4)) {
+          uint32_t d[16];
+          tmem_ld_32x32b_x16(lane_base + kColD + c0, d);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            *reinterpret_cast<uint16_t*>(stage + (c0 + c) * (kCols * 2)) = float_to_raw16<BF16>(__uint_as_float(d[c]) + bv);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the writes, before the TMA engine reads them
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_ofull));
+        if (warp == 2 + kDequantWarps && lane == 0) {
+          if (!wait_bar(&bar_ofull, ow & 1, s_abort, status)) break;
+          const int col0 = (tn * CTAS + (int)rank) * kCols;
+          if (col0 < p.N) {   // (the second CTA's columns may all lie beyond N)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(&tm_out), "r"(col0), "r"(tok0), "r"(smem_base + kOffOut) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
+          mbar_arrive(smem_u32(&bar_ofree));
+        }
+        __syncwarp();
+        ++ow;
+      } else {
+        for (int c0 = 16 * sub; c0 < p.NT; c0 += 16 * (kEpiWarps / 4)) {
+          uint32_t d[16];
+          tmem_ld_32x32b_x16(lane_base + kColD + c0, d);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; c += 4)
+            __stcg(reinterpret_cast<float4*>(slot + c0 + c), make_float4(__uint_as_float(d[c]), __uint_as_float(d[c + 1]),
+                                                                         __uint_as_float(d[c + 2]), __uint_as_float(d[c + 3])));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+        }
+      }
+      ++li;
+    }
+  }
+
+  // All roles (of both CTAs) meet here, also after a give-up: neither CTA may leave while the other can
+  // still read its shared or tensor memory or arrive on its barriers; then tensor memory is released.
+  tc_fence_before();
+  __syncthreads();
+  if (CTAS == 2) cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    if (CTAS == 2) tmem_dealloc_pair(tmem, kTmemCols); else tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// Adds, for every output tile that more than one cluster worked on, the clusters' fp32 segments in
+// cluster order, adds the bias and writes out[tok, n].  A tile is shared exactly where a boundary between
+// two clusters' ranges falls inside it, so blockIdx.x runs over the boundaries (cluster c = blockIdx.x + 1
+// against c - 1) and the first boundary inside a tile owns it; blockIdx.y runs over the tile's 32 x 32
+// blocks.  A slot is [column][token], the output [token][column]: a block goes through shared memory so that
+// both sides are coalesced.
+template <bool BF16>
+__global__ void __launch_bounds__(kFixThreads) pair_fixup_kernel(const Params p, const int ctas) {
+  __shared__ float tile[32][33];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int G = p.G;
+  const uint32_t U = p.U, C = (uint32_t)p.nclusters;
+  const uint32_t c = blockIdx.x + 1, b = range_begin(c, U, C, 1u);
+  if (b % (uint32_t)G == 0) return;                       // the boundary falls between two tiles
+  const int item = (int)(b / (uint32_t)G);
+  const int first_c = cluster_of_unit((uint32_t)item * G, U, C);
+  if (first_c != (int)c - 1) return;                       // an earlier boundary inside this tile owns it
+  const int nc = cluster_of_unit((uint32_t)item * G + G - 1, U, C) - first_c + 1;
+  const int first_slot = 2 * first_c + ((int)(range_begin(first_c, U, C, 1u) / (uint32_t)G) == item ? 0 : 1);
+  const int tn = item / p.ntt, tt = item % p.ntt;
+  const int cols = kCols * ctas;
+  const int tblocks = (p.NT + 31) / 32;
+  const int n0 = 32 * ((int)blockIdx.y / tblocks), t0 = 32 * ((int)blockIdx.y % tblocks);
+  const int tx = (int)threadIdx.x & 31, ty = (int)threadIdx.x >> 5;  // 8 rows of 32 threads
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (t0 + tx < p.NT)
+    for (int k = 0; k < nc; ++k) {
+      const float* src = p.slots + (size_t)(k == 0 ? first_slot : 2 * (first_c + k)) * p.slot_floats + t0 + tx;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] += __ldcg(src + (size_t)(n0 + ty + 8 * j) * p.NT);   // column n0 + ty + 8j, token t0 + tx
+    }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) tile[ty + 8 * j][tx] = v[j];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int row = ty + 8 * j;  // token t0 + row, column n0 + tx
+    const int tok = tt * p.NT + t0 + row, n = tn * cols + n0 + tx;
+    if (t0 + row < p.NT && tok < p.M && n < p.N) {
+      float o = tile[tx][row];
+      if (p.bias) o += bias_to_float(p.bias, p.bias_dtype, n);
+      p.out[(size_t)tok * p.N + n] = float_to_raw16<BF16>(o);
+    }
+  }
+}
+
+// The shape of the work for a problem: CTAs per cluster, tokens per tile, clusters, units.
+struct Plan { int ctas, NT, TH, ntn, ntt, nclusters, quantum; long long U, t_units; bool fixup; size_t slot_floats; };
+static Plan make_plan(int64_t M, int64_t N, int64_t K) {
+  Plan pl;
+  pl.ctas = M > 128 ? 2 : 1;
+  const int64_t cap = 128 * pl.ctas, unit = 16 * pl.ctas;   // each CTA's share is a multiple of 16 tokens
+  pl.NT = (int)(M >= cap ? cap : (M + unit - 1) / unit * unit);
+  pl.TH = pl.NT / pl.ctas;
+  pl.ntn = (int)((N + kCols * pl.ctas - 1) / (kCols * pl.ctas));
+  pl.ntt = (int)((M + pl.NT - 1) / pl.NT);
+  const int G = (int)(K / 128);
+  pl.U = (long long)pl.ntn * pl.ntt * G;
+  const long long maxc = kNumSMs / pl.ctas, items = (long long)pl.ntn * pl.ntt;
+  // Stream-K keeps every cluster busy to the end but sends the tiles that a range boundary cuts through fp32
+  // slots and a second kernel (about kFixupUnits units of time); dealing whole tiles needs neither and loses
+  // only the last wave's idle clusters.  Whichever ends first:
+  const long long t_stream = (pl.U + maxc - 1) / maxc + kFixupUnits, t_whole = (items + maxc - 1) / maxc * G;
+  const bool whole = t_whole <= t_stream;
+  pl.quantum = whole ? G : 1;
+  pl.t_units = whole ? t_whole : t_stream;
+  const long long parts = whole ? items : pl.U;
+  pl.nclusters = (int)(parts < maxc ? parts : maxc);
+  // some tile is shared between clusters unless every range boundary falls on a tile boundary
+  pl.fixup = false;
+  if (!whole && (pl.U + 1) * pl.nclusters < (1ll << 31))
+    for (int c = 1; c < pl.nclusters && !pl.fixup; ++c)
+      if (range_begin((uint32_t)c, (uint32_t)pl.U, (uint32_t)pl.nclusters, 1u) % (uint32_t)G != 0) pl.fixup = true;
+  pl.slot_floats = (size_t)kCols * pl.ctas * pl.NT;
+  return pl;
+}
+
+template <typename Kern>
+static int launch_main(Kern kern, int ctas_per_cluster, int grid, cudaStream_t st, const CUtensorMap& tw, const CUtensorMap& ts,
+                       const CUtensorMap& tz, const CUtensorMap& tx, const CUtensorMap& to, const Params& sp) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmem; cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = ctas_per_cluster; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 2;
+  if (cudaLaunchKernelEx(&cfg, kern, tw, ts, tz, tx, to, sp) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  return NQB200_OK;
+}
+
+template <bool BF16>
+static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx, const CUtensorMap& to,
+                    const Params& sp, const Plan& pl, cudaStream_t st) {
+  // The shared-memory attribute belongs to the device that is current when it is set: one flag per device.
+  static std::mutex mu;
+  static bool configured[kMaxDevices] = {false};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return NQB200_ERR_UNSUPPORTED_DEVICE; }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!configured[dev]) {
+      if (cudaFuncSetAttribute(umma_pair_kernel<BF16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
+          cudaFuncSetAttribute(umma_pair_kernel<BF16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return NQB200_ERR_LAUNCH;
+      }
+      configured[dev] = true;
+    }
+  }
+  const int grid = pl.nclusters * pl.ctas;
+  const int rc = pl.ctas == 2 ? launch_main(umma_pair_kernel<BF16, 2>, 2, grid, st, tw, ts, tz, tx, to, sp)
+                              : launch_main(umma_pair_kernel<BF16, 1>, 1, grid, st, tw, ts, tz, tx, to, sp);
+  if (rc != NQB200_OK || !pl.fixup) return rc;
+  const int blocks_per_tile = (kCols * pl.ctas / 32) * ((pl.NT + 31) / 32);
+  return launch_overlapped(pair_fixup_kernel<BF16>, dim3(pl.nclusters - 1, blocks_per_tile), dim3(kFixThreads), 0, st, sp, pl.ctas);
+}
+
+}  // namespace pair
+
+bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
+  if (!(M > 128 && g == 128 && K % 128 == 0 && N % 32 == 0)) return false;
+  // Against the single-CTA kernel (tiles of 256 columns x 128 tokens dealt to 148 CTAs with split-K, so hardly any
+  // imbalance): per unit of work this kernel is the faster by 15 %, but it deals 256 x 256 tiles to 74 pairs.
+  // It is used where its estimated time, imbalance or stream-K overhead included, stays below 1.3 x the
+  // balanced time + 15 units; over M in 192..4096 and the sweep's five shapes this rule was within 0.2 % of
+  // always picking the faster kernel.
+  const pair::Plan pl = pair::make_plan(M, N, K);
+  const long long balanced = ((N + 255) / 256) * ((M + 127) / 128) * (K / 128);   // x 1/148: units per SM
+  return 10 * 148 * pl.t_units <= 13 * balanced + 150 * 148;
+}
+
+int umma_pair_launches(int64_t M, int64_t N, int64_t K) { return pair::make_plan(M, N, K).fixup ? 2 : 1; }
+
+size_t umma_pair_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  const pair::Plan pl = pair::make_plan(M, N, K);
+  return (size_t)kCounterBytes + (pl.fixup ? (size_t)2 * pl.nclusters * pl.slot_floats * sizeof(float) : 0);
+}
+
+int launch_umma_pair(const GemmArgs& a) {
+  using namespace pair;
+  const int G = a.K / 128;
+  const Plan pl = make_plan(a.M, a.N, a.K);
+  if ((pl.U + 1) * pl.nclusters >= (1ll << 31)) return NQB200_ERR_TOO_LARGE;
+  Params sp;
+  sp.bias = a.bias; sp.bias_dtype = a.bias_dtype; sp.out = (uint16_t*)a.out;
+  sp.M = a.M; sp.N = a.N; sp.G = G;
+  sp.ntn = pl.ntn; sp.ntt = pl.ntt; sp.NT = pl.NT; sp.TH = pl.TH;
+  sp.nclusters = pl.nclusters; sp.quantum = pl.quantum; sp.U = (uint32_t)pl.U;
+  sp.status = (a.ws && a.ws_bytes >= (size_t)kCounterBytes) ? (int*)a.ws + (kCounterBytes / 4 - 1) : nullptr;
+  sp.slots = nullptr; sp.slot_floats = (int)pl.slot_floats;
+#ifdef NQ_TL
+  sp.tl = g_tl_host;
+#endif
+#ifdef NQ_TL
+  sp.tl = g_tl_host;
+#endif
+  if (pl.fixup) {
+    if (!a.ws || a.ws_bytes < umma_pair_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
+    if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
+    sp.slots = (float*)((char*)a.ws + kCounterBytes);
+  }
+  alignas(64) CUtensorMap tw, ts, tz, tx, to;
+  const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 16, CU_TENSOR_MAP_SWIZZLE_64B);
+  ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, G, a.N / 2, 1, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, G, a.N / 8, 1, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
+  ok = ok && encode_2d(&tx, xdt, 2, a.x, a.M, a.K, (uint32_t)pl.TH, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && encode_2d(&to, xdt, 2, a.out, a.M, a.N, (uint32_t)pl.NT, kCols, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (!ok) return NQB200_ERR_LAUNCH;
+  return a.dtype == NQB200_BF16 ? launch_t<true>(tw, ts, tz, tx, to, sp, pl, a.stream)
+                                : launch_t<false>(tw, ts, tz, tx, to, sp, pl, a.stream);
+}
+
+}  // namespace nqb200

@@ -257,6 +257,49 @@ def test_gemm_sweep_every_point_vs_oracle(K, N, dtype, M):
     _lib.check_workspaces()  # no bounded wait gave up
 
 
+# The two-CTA tcgen05 kernel at ragged sizes: token counts that end inside a 256-token tile, a column count whose
+# last 256-column tile holds 32 columns (the second CTA of the pair then has none), whole-tile dealing and stream-K
+# with its second kernel, with and without bias.  The case list pins which kernel and how many launches the
+# dispatch picks, so that a change of the rule cannot silently take these paths out of the test.
+@pytest.mark.parametrize("M,K,N,dtype,bias,launches", [
+    (777, 4096, 12288, torch.float16, True, 1),
+    (1000, 1024, 25632, torch.float16, False, 1),
+    (1000, 1024, 25632, torch.bfloat16, True, 1),
+    (1100, 25600, 5152, torch.float16, True, 2),
+    (4096, 25600, 5120, torch.bfloat16, True, 2),
+    (700, 5120, 25600, torch.bfloat16, False, 1),
+])
+def test_gemm_pair_kernel_ragged(M, K, N, dtype, bias, launches):
+    lib = _lib.load()
+    code = 0 if dtype == torch.float16 else 1
+    assert lib.nqb200_gemm_kernel_name(M, N, K, 128, code) == b"prefill_tcgen05_pair"
+    assert lib.nqb200_gemm_launch_count(M, N, K, 128, code) == launches
+    g = torch.Generator().manual_seed(M + N)
+    qw = torch.randint(-2 ** 31, 2 ** 31, (K, N // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    qz = torch.randint(-2 ** 31, 2 ** 31, (K // 128, N // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    sc = (torch.rand(K // 128, N, generator=g) * 9e-3 + 1e-3).to(dtype)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(N, generator=g).to(dtype) if bias else None
+    # sentinel rows around the output: a store that runs past M tokens would change them
+    m = nq.WQLinear_GEMM(4, 128, K, N, DEV, bias, dtype)
+    m.qweight.copy_(qw); m.qscales.copy_(sc); m.qzeros.copy_(qz)
+    if bias:
+        m.bias.copy_(b)
+    buf = torch.full((M + 2, N), -7.25, dtype=dtype, device=DEV)
+    y = m(x.to(DEV), out=buf[1:M + 1])
+    torch.cuda.synchronize()
+    assert bool((buf[0] == -7.25).all()) and bool((buf[M + 1] == -7.25).all())
+    rows = torch.cat([torch.tensor([0, 255, 256, M - 1]), torch.randperm(M, generator=g)[:28]])
+    W = O.dequantize(qw, sc, qz)
+    ref = x[rows].float() @ W.float()
+    if b is not None:
+        ref = ref + b.float()
+    err = O.rel_err(y[rows.to(DEV)], ref)
+    assert err <= (TIGHT if dtype == torch.float16 else 8e-3), f"rel err {err:.3e}"
+    assert bool(torch.isfinite(y.float()).all())
+    _lib.check_workspaces()
+
+
 def test_gemm_linearity_property_full_size():
     # size-independent property at a full benchmark shape: y(2x) == 2*y(x) exactly in fp16
     c = O.make_case(5120, 25600, 4, seed=3)
