@@ -274,36 +274,66 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       const uint64_t desc0 = umma_smem_desc_sw128(smem_base);
       const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
       const uint32_t x1 = ((uint32_t)p.TH * 128u) >> 4;          // second activation box, in the descriptor's 16-byte units
+      // The MMA queue is short (the tensor pipe ran dry during the 300 ns that this thread spent between two
+      // units on waits, the completion report and loop bookkeeping), so the loop is software-pipelined: the
+      // next unit's barrier is polled and the previous unit's completion is reported between MMAs of the
+      // current unit, while MMAs are queued.  A report therefore also covers the next unit's first two
+      // MMAs and frees its stage about 160 ns later than it could, which four stages absorb.
       uint32_t s = 0, phase = 0;
-      int gk = (int)(u_begin % (uint32_t)G), li = 0;
+      int gk = (int)(u_begin % (uint32_t)G), li = 0, pending = -1;
       bool first = true;
-      for (uint32_t u = u_begin; u < u_end; ++u) {
-        const bool last = gk == G - 1 || u == u_end - 1;
-        if (first && li > 0 && !wait_bar(&bar_dempty, (li - 1) & 1, s_abort, status)) break;   // the epilogues drained D
-        if (!wait_bar(&bar_xfull[s], phase, s_abort, status)) break;
-        if (!wait_bar(&bar_afull[s], phase, s_abort, status)) break;   // (both CTAs') A slot filled, activations landed
+      bool ok = nunits > 0 && wait_bar(&bar_afull[0], 0, s_abort, status);   // (both CTAs') A slot filled, activations landed
+      const uint32_t d = tmem + kColD;
+      auto mma = [&](uint32_t lo, uint32_t a, int ks, uint32_t acc) {
+        const uint32_t dlo = lo + (ks >> 2) * x1 + (ks & 3) * 2;
+        if (CTAS == 2) umma_ts_pair_lohi(d, a + ks * 8, dlo, desc_hi, idesc, acc);
+        else umma_ts_lohi(d, a + ks * 8, dlo, desc_hi, idesc, acc);
+      };
+      auto report = [&](uint64_t* bar) {
+        if (CTAS == 2) umma_commit_pair_both(smem_u32(bar), 3); else umma_commit(smem_u32(bar));
+      };
+      for (uint32_t u = u_begin; ok && u < u_end; ++u) {
+        const bool last = gk == G - 1 || u == u_end - 1, more = u + 1 < u_end;
+#ifdef NQ_TL
+        const int ti = (int)(u - u_begin);
+        const bool tl_on = p.tl && blockIdx.x == 0 && ti < 256;
+        if (tl_on) p.tl[512 + 4 * ti] = (unsigned long long)clock64();
+#endif
         tc_fence_after();
         const uint32_t lo = desc_lo0 + s * (uint32_t)(kXStageBytes >> 4);
-        const uint32_t a = tmem + kColA + s * 64, d = tmem + kColD;
+        const uint32_t a = tmem + kColA + s * 64;
+        mma(lo, a, 0, first ? 0u : 1u);
+        mma(lo, a, 1, 1u);
+#ifdef NQ_TL
+        if (tl_on) p.tl[512 + 4 * ti + 2] = (unsigned long long)clock64();
+#endif
+        if (pending >= 0) { report(&bar_done[pending]); pending = -1; }
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t dlo = lo + (ks >> 2) * x1 + (ks & 3) * 2;
-          const uint32_t acc = ks > 0 ? 1u : (first ? 0u : 1u);
-          if (CTAS == 2) umma_ts_pair_lohi(d, a + ks * 8, dlo, desc_hi, idesc, acc);
-          else umma_ts_lohi(d, a + ks * 8, dlo, desc_hi, idesc, acc);
-        }
-        if (CTAS == 2) {
-          umma_commit_pair_both(smem_u32(&bar_done[s]), 3);
-          if (last) umma_commit_pair_both(smem_u32(&bar_dfull), 3);
+        for (int ks = 2; ks < 6; ++ks) mma(lo, a, ks, 1u);
+        const uint32_t sn = s + 1 == kXStages ? 0u : s + 1, phn = s + 1 == kXStages ? phase ^ 1u : phase;
+        const bool ready = more && !last && mbar_try_wait(smem_u32(&bar_afull[sn]), phn);
+        mma(lo, a, 6, 1u);
+        mma(lo, a, 7, 1u);
+#ifdef NQ_TL
+        if (tl_on) p.tl[512 + 4 * ti + 3] = (unsigned long long)clock64();
+#endif
+        if (last) {
+          report(&bar_done[s]);
+          report(&bar_dfull);
+          ++li;
+          if (more) ok = wait_bar(&bar_dempty, (li - 1) & 1, s_abort, status);   // the epilogues drained D
         } else {
-          umma_commit(smem_u32(&bar_done[s]));
-          if (last) umma_commit(smem_u32(&bar_dfull));
+          pending = (int)s;
         }
-        if (last) ++li;
+        if (more && !ready && ok) ok = wait_bar(&bar_afull[sn], phn, s_abort, status);
+#ifdef NQ_TL
+        if (tl_on) p.tl[512 + 4 * ti + 1] = (unsigned long long)clock64() | ((unsigned long long)(ready ? 1 : 0) << 62);
+#endif
         first = last;
         if (++gk == G) gk = 0;
-        if (++s == kXStages) { s = 0; phase ^= 1u; }
+        s = sn; phase = phn;
       }
+      if (pending >= 0) report(&bar_done[pending]);
       // everything issued has completed before tensor memory may be released
       if (CTAS == 2) umma_commit_pair(map_to_cta(smem_u32(&bar_drain), 0)); else umma_commit(smem_u32(&bar_drain));
       mbar_wait(smem_u32(&bar_drain), 0);
@@ -418,18 +448,32 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         // at M and N.  The accumulator is handed back as soon as it has been read.
         if (ow > 0 && !wait_bar(&bar_ofree, (ow - 1) & 1, s_abort, status)) break;   // the previous store has read the staging area
         uint8_t* stage = smem_raw + (smem_base - smem_u32(smem_raw)) + kOffOut + n_local * 2;
-        for (int c0 = 16 * sub; c0 < p.NT; c0 += 16 * (kEpiWarps / 4)) {
+        // The accumulator is handed back right after the last read, before the last values are converted:
+        // the tensor pipe idles from the tile's last MMA until then.
+        constexpr int kStep = 16 * (kEpiWarps / 4);
+        bool handed_back = false;
+        for (int c0 = 16 * sub; c0 < p.NT; c0 += kStep) {
           uint32_t d[16];
           tmem_ld_32x32b_x16(lane_base + kColD + c0, d);
           tc_wait_ld();
+          if (c0 + kStep >= p.NT) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+            }
+            handed_back = true;
+          }
 #pragma unroll
           for (int c = 0; c < 16; ++c)
             *reinterpret_cast<uint16_t*>(stage + (c0 + c) * (kCols * 2)) = float_to_raw16<BF16>(__uint_as_float(d[c]) + bv);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+        if (!handed_back) {   // (a tile of so few tokens that this warp had none)
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the writes, before the TMA engine reads them
         __syncwarp();
