@@ -1,57 +1,45 @@
-// Prefill kernel on the 5th-generation tensor cores: W4A16 GEMM for more than
-// 16 tokens, group size 128.
+// Prefill kernel for many tokens on the 5th-generation tensor cores: W4A16 GEMM, group size 128, two SMs per
+// tile (tcgen05.mma.cta_group::2).  Replaces what the reference does from 256 tokens on -- a Triton kernel that
+// writes the dense 16-bit weight to HBM, then torch.matmul (nanoquantization/layers/gemm.py:10-123, 552-567) --
+// with one kernel that never materialises the dense weight.
 //
 //   D[n, tok] (TMEM, fp32) = sum_k W[k, n] (TMEM, 16-bit) * x[tok, k] (smem)
 //
-// The weights are the 128-row A operand, dequantised to their true 16-bit
-// values (q - z) * s -- the integer difference first, then one multiply, which
-// is the reference's rounding -- straight from registers into tensor memory;
-// the tokens are the N dimension of the MMA, read from shared memory as a
-// K-major operand that TMA wrote with the 128-byte swizzle.  A packed word
-// never touches shared memory again after the TMA load, and a dequantised
-// value never touches shared memory at all.
+// The weights are the A operand, dequantised to their true 16-bit values (q - z) * s -- the integer difference
+// first, then one multiply, which is the reference's rounding -- straight from registers into tensor memory; the
+// tokens are the N dimension of the MMA, read from shared memory as a K-major operand that TMA wrote with the
+// 128-byte swizzle.  A dequantised value never touches shared memory.
 //
-// What bounds this kernel is the dequantisation (about 15 ALU instructions per
-// packed word), so a dequantised weight must feed as many tokens as possible:
-// a CTA owns 128 weight columns (one A block: 64 columns of tensor memory per
-// 128-k slot, four slots, one per stage of the activation ring) and accumulates up to 256 tokens at once (D: 256
-// columns of tensor memory).  Above 128 tokens two CTAs of a cluster (the two
-// SMs of a TPC) work as one: tcgen05.mma.cta_group::2 with M = 256 (128 weight
-// columns from each CTA's tensor memory) and N = up to 256 tokens, of which each
-// CTA loads only its half of the activation tile.  Per CTA and 128-k group that
-// is 8 KB of packed weights and at most 32 KB of activations for 1024 cycles of
-// tensor-core work.  Up to 128 tokens a CTA works alone (cta_group::1, N =
-// tokens rounded up to 16).
+// A dequantised weight should feed as many tokens as possible, and the activations should be fetched as rarely as
+// possible.  The two CTAs of a cluster (the two SMs of a TPC) work as one: M = 256 weight columns (128 from each
+// CTA's tensor memory: one A block of 64 columns per 128-k slot, four slots) by N = up to 256 tokens, of which each
+// CTA loads only its half.  Per CTA and 128-k unit: 8.5 KB of packed weights, scales and zero-points, at most
+// 32 KB of activations, and 8 MMAs of about 141 cycles.  Tensor memory is full: 256 columns of A ring and 256 of
+// accumulator, so the accumulator is single and the tensor pipe idles while the epilogue reads it (about 2 us per
+// tile); the epilogue therefore only moves the tile into shared memory, 16-bit, and one TMA store writes it out.
 //
-// Work is dealt as stream-K: a unit is one 128-k group of one output tile
-// (128 x CTAs weight columns by NT tokens); cluster c takes the contiguous
-// range [c U / C, (c + 1) U / C) of units, token tiles fastest so that
-// neighbours share packed weights in L2.  A segment that covers a tile's whole
-// K is written to the output by the epilogue; other segments go to fp32 slots
-// (two per cluster) and a second kernel adds a tile's segments in cluster order
-// (results do not depend on timing), adds the bias and writes the output.
+// Work: a unit is one 128-k group of one output tile; cluster c takes a contiguous range of units, token tiles
+// fastest so that neighbours share packed weights in L2.  Either ranges end on tile boundaries (whole tiles), or
+// they are equal (stream-K) and a tile that a boundary cuts leaves as fp32 segments, which a second kernel adds in
+// cluster order (results do not depend on timing) together with the bias.  The host picks whichever its cost model
+// says ends first (make_plan).
 //
-//   warps 0, 30   TMA producers: two boxes of activations (128-byte swizzle) per unit
-//                 into a ring of four stages; 128 x 64 B of packed weights (64-byte
-//                 swizzle) with the group's scales and zero-points into a ring of
-//                 eight, freed by the dequantisers, so weights are fetched far ahead.
-//   warp 1        MMA issuer (the leader CTA's, for a pair): per k-step one
-//                 tcgen05.mma (M = 128 or 256, N = tokens, K = 16), accumulating
-//                 over the segment's K in tensor memory.
-//   warps 2-17    dequantisers, two sets of 8 taking alternate units.  Warp
-//                 (lane quarter q, k half h) takes the 32 columns of chunk q for
-//                 k-steps 4h..4h+3: ldmatrix.x2.trans gives a thread four nibbles
-//                 of row k and of row k+1 per register (the k pairs of the
-//                 operand layout); masks make 1024+q (1024+16q for the odd
-//                 nibbles, 128+q in bf16), a subtract (or fma by 1/16) removes
-//                 offset and zero-point exactly, a multiply applies the scale;
-//                 tcgen05.st.16x128b.x2 puts them into 16 lanes of the A slot.
-//   warps 18-29   epilogue at the end of a segment: D -> registers -> out[tok, n]
-//                 (+ bias, 16-bit) or the fp32 slot.
+//   warp 0        TMA producer of the activations: two boxes per unit into a ring of four stages.
+//   warp 30       TMA producer of the packed weights (64-byte swizzle), scales and zero-points: a ring of three
+//                 stages, freed as soon as the dequantisers have read them.
+//   warp 1        MMA issuer (the leader CTA's): 8 tcgen05.mma per unit, software-pipelined (see there).
+//   warps 2-17    dequantisers, two sets of 8 taking alternate units.  Warp (lane quarter q, k half h) takes the
+//                 32 columns of chunk q for k-steps 4h..4h+3: ldmatrix.x2.trans gives a thread four nibbles of
+//                 row k and of row k+1 per register (the k pairs of the operand layout); masks make 1024+q
+//                 (1024+16q for the odd nibbles, 128+q in bf16), a subtract (or fma by 1/16) removes offset and
+//                 zero-point exactly, a multiply applies the scale; tcgen05.st.16x128b.x2 puts them into 16 lanes
+//                 of the A slot.
+//   warps 18-29   epilogue: accumulator -> registers -> (+ bias, 16-bit) shared memory -> TMA store, or the fp32
+//                 segment of a cut tile.
 //
-// Every wait is bounded; on expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in
-// the workspace status word, all roles drain, both CTAs of a pair meet at the
-// closing cluster barrier, and tensor memory is released.
+// Every wait is bounded; on expiry the kernel records NQB200_ERR_WAIT_TIMEOUT in the workspace status word, all
+// roles drain, both CTAs meet at the closing cluster barrier, and tensor memory is released.  A wait on a phase
+// parity is only right for a waiter that has seen the phase before it: see kWBars.
 #include "common.cuh"
 #include "tma_utils.cuh"
 #include "umma_utils.cuh"
@@ -111,22 +99,20 @@ struct Params {
 #endif
 };
 
-// `sleep_ns` > 0: back off between polls (roles that wait long should not take issue slots).
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                         unsigned sleep_ns = 0) {
+// A wait suspends in hardware for up to kSuspendNs at a time (woken at once when the phase completes), so the
+// 31 warps that wait most of the time hardly issue; the limit is checked against the clock after each suspension.
+constexpr uint32_t kSuspendNs = 20000;
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
   const uint32_t b = smem_u32(bar);
-  if (mbar_try_wait(b, parity)) return true;
+  if (mbar_test_wait(b, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(b, parity)) return true;
-    if (sleep_ns) __nanosleep(sleep_ns);
-    if ((i & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        if (status) atomicExch(status, NQB200_ERR_WAIT_TIMEOUT);
-        return false;
-      }
+  for (;;) {
+    if (mbar_try_wait_suspend(b, parity, kSuspendNs)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      if (status) atomicExch(status, NQB200_ERR_WAIT_TIMEOUT);
+      return false;
     }
   }
 }
@@ -311,7 +297,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
         for (int ks = 2; ks < 6; ++ks) mma(lo, a, ks, 1u);
         const uint32_t sn = s + 1 == kXStages ? 0u : s + 1, phn = s + 1 == kXStages ? phase ^ 1u : phase;
-        const bool ready = more && !last && mbar_try_wait(smem_u32(&bar_afull[sn]), phn);
+        const bool ready = more && !last && mbar_test_wait(smem_u32(&bar_afull[sn]), phn);
         mma(lo, a, 6, 1u);
         mma(lo, a, 7, 1u);
 #ifdef NQ_TL
@@ -434,7 +420,7 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       const int g1 = g0 + (int)(seg_end - u);
       u = seg_end;
       const int tn = item / p.ntt, tt = item % p.ntt;
-      if (!wait_bar(&bar_dfull, li & 1, s_abort, status, 200)) break;
+      if (!wait_bar(&bar_dfull, li & 1, s_abort, status)) break;
       tc_fence_after();
       const bool whole = g0 == 0 && g1 == G;
       const int n = (tn * CTAS + (int)rank) * kCols + n_local;
@@ -574,7 +560,7 @@ __global__ void __launch_bounds__(kFixThreads) pair_fixup_kernel(const Params p,
 struct Plan { int ctas, NT, TH, ntn, ntt, nclusters, quantum; long long U, t_units; bool fixup; size_t slot_floats; };
 static Plan make_plan(int64_t M, int64_t N, int64_t K) {
   Plan pl;
-  pl.ctas = M > 128 ? 2 : 1;
+  pl.ctas = 2;
   const int64_t cap = 128 * pl.ctas, unit = 16 * pl.ctas;   // each CTA's share is a multiple of 16 tokens
   pl.NT = (int)(M >= cap ? cap : (M + unit - 1) / unit * unit);
   pl.TH = pl.NT / pl.ctas;
@@ -627,8 +613,7 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
   {
     std::lock_guard<std::mutex> lock(mu);
     if (!configured[dev]) {
-      if (cudaFuncSetAttribute(umma_pair_kernel<BF16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
-          cudaFuncSetAttribute(umma_pair_kernel<BF16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
+      if (cudaFuncSetAttribute(umma_pair_kernel<BF16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
         cudaGetLastError();
         return NQB200_ERR_LAUNCH;
       }
@@ -636,8 +621,7 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
     }
   }
   const int grid = pl.nclusters * pl.ctas;
-  const int rc = pl.ctas == 2 ? launch_main(umma_pair_kernel<BF16, 2>, 2, grid, st, tw, ts, tz, tx, to, sp)
-                              : launch_main(umma_pair_kernel<BF16, 1>, 1, grid, st, tw, ts, tz, tx, to, sp);
+  const int rc = launch_main(umma_pair_kernel<BF16, 2>, 2, grid, st, tw, ts, tz, tx, to, sp);
   if (rc != NQB200_OK || !pl.fixup) return rc;
   const int blocks_per_tile = (kCols * pl.ctas / 32) * ((pl.NT + 31) / 32);
   return launch_overlapped(pair_fixup_kernel<BF16>, dim3(pl.nclusters - 1, blocks_per_tile), dim3(kFixThreads), 0, st, sp, pl.ctas);
