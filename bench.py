@@ -174,10 +174,24 @@ def run_ours(args):
             raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    stage = ["set-up"]
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner out of stdout: one JSON line only
+        # A rank may leave through a watchdog below while others are still inside a collective: keep NCCL off
+        # NVLink multicast objects, which a vanished rank must not be bound to.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+
+        def give_up():
+            # a multi-rank run that has not finished by now is stuck (one rank failed, the others wait for it)
+            if rank == 0:
+                emit(json.dumps({"metric": "w4a16_gemm_sweep_us", "n_gpus": world, "impl": "ours",
+                                 "unavailable": f"the run did not finish within {args.max_seconds} s (stage: {stage[0]})"}))
+            os._exit(0)
+        overall = threading.Timer(args.max_seconds, give_up)
+        overall.daemon = True
+        overall.start()
     dtype = torch.float16
     lib = _lib.load()
     assert lib.nqb200_device_supported(local) == 1, "not a B200"
@@ -308,10 +322,12 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    stage[0] = "timed sweep"
     ms_dev = timed(run_sweep, args.steps)
     ms_e2e = timed(sweep_e2e, args.steps, e2e_begin, e2e_end)
 
     # per-point pass: each point launched back to back over rotating weight copies
+    stage[0] = "per-point pass"
     per_point = []
     for (si, M) in points:
         K, N, kind = SHAPES[si]
@@ -345,6 +361,7 @@ def run_ours(args):
                 for lin in layers[si]:
                     if hasattr(lin, "attach_comm"):
                         lin.attach_comm(None)
+        stage[0] = "tp_parity"
         tp_parity = tp_parity_leg(world, rank, dev, dtype, comm)
         barrier()
     sweep_graph = fn = None  # graphs hold captured collectives: dropped well before the process group is destroyed
@@ -353,19 +370,12 @@ def run_ours(args):
         for k in list(layers):
             del layers[k]
         torch.cuda.empty_cache()
+        stage[0] = "decode_qwen3_8b"
         decode = decode_bench(world, rank, dev, dtype)
         barrier()
         if world == 1:
             torch.cuda.empty_cache()
             small = engine_bench_0p6b(dev, dtype)
-        if world == 8 and not args.no_serve:
-            # the largest configuration: Qwen3-32B architecture, 256 requests, continuous batching, on all 8 GPUs
-            torch.cuda.empty_cache()
-            try:
-                serve = serve_bench(world, rank, dev, dtype)
-            except Exception as exc:  # the sweep's numbers stand whatever happens here
-                serve = {"error": f"{type(exc).__name__}: {exc}"[:300]}
-            barrier()
 
     if rank == 0:
         pk = peaks()
@@ -422,14 +432,47 @@ def run_ours(args):
             line["reference_gpu"] = ref_gpu
         if tp_parity is not None:
             line["tp_parity"] = tp_parity
-        if serve is not None:
-            line["serve_qwen3_32b"] = serve
         if world == 1:
             line["cpu_baseline"] = cpu_baseline()
+    if world == 8 and not args.no_serve and not args.no_decode:
+        # The largest configuration: Qwen3-32B architecture, 256 requests, continuous batching, on all 8 GPUs.  The
+        # line above stands whatever happens here: past its time budget every rank leaves, rank 0 printing the line
+        # without this part (ranks that wait in a collective for one that failed would wait for NCCL's own
+        # time-out, ten minutes).
+        stage[0] = "serve"
+        lock, printed = threading.Lock(), [False]
+
+        def serve_over_budget():
+            with lock:
+                if printed[0]:
+                    return
+                printed[0] = True
+                if rank == 0:
+                    line["serve_qwen3_32b"] = {"unavailable": f"did not finish within {args.serve_budget} s"}
+                    emit(json.dumps(line))
+            os._exit(0)
+        timer = threading.Timer(args.serve_budget, serve_over_budget)
+        timer.daemon = True
+        timer.start()
+        torch.cuda.empty_cache()
+        try:
+            serve = serve_bench(world, rank, dev, dtype)
+        except Exception as exc:
+            serve = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        barrier()
+        with lock:
+            printed[0] = True
+        timer.cancel()
+        if rank == 0:
+            line["serve_qwen3_32b"] = serve
+    if rank == 0:
         emit(json.dumps(line))
+    stage[0] = "teardown"
     if comm is not None:
         comm.close()
     leave_distributed(world)
+    if world > 1:
+        overall.cancel()
 
 
 def sweep_config(parallelism, launch):
@@ -973,6 +1016,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the Qwen3-8B decode tokens/s section")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's own GPU path (1 GPU)")
     ap.add_argument("--no-serve", action="store_true", help="with --gpus 8: skip the Qwen3-32B continuous-batching workload")
+    ap.add_argument("--serve-budget", type=int, default=240, help="seconds the --gpus 8 serving workload may take before the line is printed without it")
+    ap.add_argument("--max-seconds", type=int, default=840, help="a multi-GPU run that has not finished by then prints an `unavailable` line and leaves")
     ap.add_argument("--nccl-only", action="store_true", help="tensor parallel: all-reduce through NCCL only")
     ap.add_argument("--reference-budget", type=float, default=330.0,
                     help="--impl reference: wall-clock seconds after which no further pass is started")
