@@ -83,6 +83,7 @@ constexpr int kSmem = kOffOut + kOutBytes + 1024;
 constexpr uint32_t kWStageTx = 8192 + 256 + 64;
 constexpr int kColA = 0, kColD = 256, kTmemCols = 512;
 constexpr int kFixThreads = 256;
+constexpr int kSlotRows = 256;     // token rows of an fp32 slot (whatever the tile's token count), 256 columns each
 constexpr int kFixupUnits = 55;   // measured: 30 to 60 us, a unit being about 1 us
 
 struct Params {
@@ -92,7 +93,7 @@ struct Params {
   int NT, TH;          // tokens per tile (the MMA's N) and per CTA (NT / CTAs)
   int nclusters, quantum;   // quantum: 1 (stream-K) or G (a cluster takes whole tiles)
   uint32_t U;          // units: ntn * ntt * G
-  float* slots; int slot_floats;  // [2 * nclusters][CTAs * 128][NT] fp32
+  float* slots; int slot_floats;  // [2 * nclusters][kSlotRows tokens][CTAs * 128 columns] fp32
   int* status;         // may be null
 #ifdef NQ_TL
   unsigned long long* tl;
@@ -152,7 +153,7 @@ template <bool BF16, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_sc,
                     const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_x,
-                    const __grid_constant__ CUtensorMap tm_out, const Params p) {
+                    const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_slot, const Params p) {
   constexpr uint32_t LO = 0x000F000Fu, HI = 0x00F000F0u;
   constexpr uint32_t MAGIC = BF16 ? 0x43004300u : 0x64006400u;  // 128.0 / 1024.0 in both halves
   constexpr uint32_t SIXTEENTH = 0x2C002C00u;                   // 1/16 in both halves (fp16)
@@ -426,8 +427,6 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       const int n = (tn * CTAS + (int)rank) * kCols + n_local;
       const bool n_ok = n < p.N;
       const int tok0 = tt * p.NT;
-      float* slot = p.slots + ((size_t)cluster_id * 2 + (item == first_item ? 0 : 1)) * p.slot_floats +
-                    (size_t)((int)rank * kCols + n_local) * p.NT;
       const float bv = (whole && p.bias && n_ok) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
       if (whole) {
         // The tile leaves through shared memory: [token][column] in 16 bits, written by one TMA store that clips
@@ -478,19 +477,53 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         __syncwarp();
         ++ow;
       } else {
-        for (int c0 = 16 * sub; c0 < p.NT; c0 += 16 * (kEpiWarps / 4)) {
-          uint32_t d[16];
-          tmem_ld_32x32b_x16(lane_base + kColD + c0, d);
-          tc_wait_ld();
+        // A segment of a tile that another cluster shares: fp32 to this cluster's slot, [token][column], in two
+        // halves of 128 tokens through the same staging area (64 KB hold 128 x 128 fp32), one TMA store each.
+        constexpr int kStep = 16 * (kEpiWarps / 4);
+        const int slot_row = ((int)cluster_id * 2 + (item == first_item ? 0 : 1)) * kSlotRows;
+        uint8_t* stage = smem_raw + (smem_base - smem_u32(smem_raw)) + kOffOut + n_local * 4;
+        bool handed_back = false, gave_up = false;
+        for (int h = 0; 128 * h < p.NT && !gave_up; ++h) {
+          if (ow > 0 && !wait_bar(&bar_ofree, (ow - 1) & 1, s_abort, status)) { gave_up = true; break; }
+          const int t_lo = 128 * h, t_hi = min(t_lo + 128, p.NT);
+          for (int c0 = 16 * sub; c0 < t_hi; c0 += kStep) {
+            if (c0 < t_lo) continue;
+            uint32_t d[16];
+            tmem_ld_32x32b_x16(lane_base + kColD + c0, d);
+            tc_wait_ld();
+            if (c0 + kStep >= p.NT) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+              }
+              handed_back = true;
+            }
 #pragma unroll
-          for (int c = 0; c < 16; c += 4)
-            __stcg(reinterpret_cast<float4*>(slot + c0 + c), make_float4(__uint_as_float(d[c]), __uint_as_float(d[c + 1]),
-                                                                         __uint_as_float(d[c + 2]), __uint_as_float(d[c + 3])));
+            for (int c = 0; c < 16; ++c) *reinterpret_cast<uint32_t*>(stage + (c0 - t_lo + c) * (kCols * 4)) = d[c];
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bar_ofull));
+          if (warp == 2 + kDequantWarps && lane == 0) {
+            if (wait_bar(&bar_ofull, ow & 1, s_abort, status)) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&tm_slot), "r"((int)rank * kCols), "r"(slot_row + t_lo), "r"(smem_base + kOffOut) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              mbar_arrive(smem_u32(&bar_ofree));
+            }
+          }
+          __syncwarp();
+          ++ow;
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+        if (gave_up) break;
+        if (!handed_back) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (CTAS == 2) mbar_arrive_cluster(dempty_addr); else mbar_arrive(dempty_addr);
+          }
         }
       }
       ++li;
@@ -512,12 +545,10 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 // Adds, for every output tile that more than one cluster worked on, the clusters' fp32 segments in
 // cluster order, adds the bias and writes out[tok, n].  A tile is shared exactly where a boundary between
 // two clusters' ranges falls inside it, so blockIdx.x runs over the boundaries (cluster c = blockIdx.x + 1
-// against c - 1) and the first boundary inside a tile owns it; blockIdx.y runs over the tile's 32 x 32
-// blocks.  A slot is [column][token], the output [token][column]: a block goes through shared memory so that
-// both sides are coalesced.
+// against c - 1) and the first boundary inside a tile owns it; blockIdx.y runs over the tile's blocks of
+// 32 tokens x 32 columns.  Slots and output are both [token][column]: a warp reads and writes rows of 32.
 template <bool BF16>
 __global__ void __launch_bounds__(kFixThreads) pair_fixup_kernel(const Params p, const int ctas) {
-  __shared__ float tile[32][33];
   grid_launch_dependents();
   grid_dependency_wait();
   const int G = p.G;
@@ -534,25 +565,21 @@ __global__ void __launch_bounds__(kFixThreads) pair_fixup_kernel(const Params p,
   const int tblocks = (p.NT + 31) / 32;
   const int n0 = 32 * ((int)blockIdx.y / tblocks), t0 = 32 * ((int)blockIdx.y % tblocks);
   const int tx = (int)threadIdx.x & 31, ty = (int)threadIdx.x >> 5;  // 8 rows of 32 threads
+  const int n = tn * cols + n0 + tx;
   float v[4] = {0.f, 0.f, 0.f, 0.f};
-  if (t0 + tx < p.NT)
-    for (int k = 0; k < nc; ++k) {
-      const float* src = p.slots + (size_t)(k == 0 ? first_slot : 2 * (first_c + k)) * p.slot_floats + t0 + tx;
+  for (int k = 0; k < nc; ++k) {
+    const float* src = p.slots + (size_t)(k == 0 ? first_slot : 2 * (first_c + k)) * p.slot_floats + n0 + tx;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] += __ldcg(src + (size_t)(n0 + ty + 8 * j) * p.NT);   // column n0 + ty + 8j, token t0 + tx
+    for (int j = 0; j < 4; ++j) {
+      const int row = t0 + ty + 8 * j;
+      if (row < p.NT) v[j] += __ldcg(src + (size_t)row * cols);
     }
-#pragma unroll
-  for (int j = 0; j < 4; ++j) tile[ty + 8 * j][tx] = v[j];
-  __syncthreads();
+  }
+  const float bv = (p.bias && n < p.N) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const int row = ty + 8 * j;  // token t0 + row, column n0 + tx
-    const int tok = tt * p.NT + t0 + row, n = tn * cols + n0 + tx;
-    if (t0 + row < p.NT && tok < p.M && n < p.N) {
-      float o = tile[tx][row];
-      if (p.bias) o += bias_to_float(p.bias, p.bias_dtype, n);
-      p.out[(size_t)tok * p.N + n] = float_to_raw16<BF16>(o);
-    }
+    const int row = t0 + ty + 8 * j, tok = tt * p.NT + row;
+    if (row < p.NT && tok < p.M && n < p.N) p.out[(size_t)tok * p.N + n] = float_to_raw16<BF16>(v[j] + bv);
   }
 }
 
@@ -583,13 +610,13 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K) {
   if (!whole && (pl.U + 1) * pl.nclusters < (1ll << 31))
     for (int c = 1; c < pl.nclusters && !pl.fixup; ++c)
       if (range_begin((uint32_t)c, (uint32_t)pl.U, (uint32_t)pl.nclusters, 1u) % (uint32_t)G != 0) pl.fixup = true;
-  pl.slot_floats = (size_t)kCols * pl.ctas * pl.NT;
+  pl.slot_floats = (size_t)kCols * pl.ctas * kSlotRows;
   return pl;
 }
 
 template <typename Kern>
 static int launch_main(Kern kern, int ctas_per_cluster, int grid, cudaStream_t st, const CUtensorMap& tw, const CUtensorMap& ts,
-                       const CUtensorMap& tz, const CUtensorMap& tx, const CUtensorMap& to, const Params& sp) {
+                       const CUtensorMap& tz, const CUtensorMap& tx, const CUtensorMap& to, const CUtensorMap& tsl, const Params& sp) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmem; cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -598,13 +625,13 @@ static int launch_main(Kern kern, int ctas_per_cluster, int grid, cudaStream_t s
   attr[1].id = cudaLaunchAttributeClusterDimension;
   attr[1].val.clusterDim.x = ctas_per_cluster; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 2;
-  if (cudaLaunchKernelEx(&cfg, kern, tw, ts, tz, tx, to, sp) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
+  if (cudaLaunchKernelEx(&cfg, kern, tw, ts, tz, tx, to, tsl, sp) != cudaSuccess) { cudaGetLastError(); return NQB200_ERR_LAUNCH; }
   return NQB200_OK;
 }
 
 template <bool BF16>
 static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensorMap& tz, const CUtensorMap& tx, const CUtensorMap& to,
-                    const Params& sp, const Plan& pl, cudaStream_t st) {
+                    const CUtensorMap& tsl, const Params& sp, const Plan& pl, cudaStream_t st) {
   // The shared-memory attribute belongs to the device that is current when it is set: one flag per device.
   static std::mutex mu;
   static bool configured[kMaxDevices] = {false};
@@ -621,7 +648,7 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
     }
   }
   const int grid = pl.nclusters * pl.ctas;
-  const int rc = launch_main(umma_pair_kernel<BF16, 2>, 2, grid, st, tw, ts, tz, tx, to, sp);
+  const int rc = launch_main(umma_pair_kernel<BF16, 2>, 2, grid, st, tw, ts, tz, tx, to, tsl, sp);
   if (rc != NQB200_OK || !pl.fixup) return rc;
   const int blocks_per_tile = (kCols * pl.ctas / 32) * ((pl.NT + 31) / 32);
   return launch_overlapped(pair_fixup_kernel<BF16>, dim3(pl.nclusters - 1, blocks_per_tile), dim3(kFixThreads), 0, st, sp, pl.ctas);
@@ -671,16 +698,20 @@ int launch_umma_pair(const GemmArgs& a) {
     if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
     sp.slots = (float*)((char*)a.ws + kCounterBytes);
   }
-  alignas(64) CUtensorMap tw, ts, tz, tx, to;
+  alignas(64) CUtensorMap tw, ts, tz, tx, to, tsl;
   const CUtensorMapDataType xdt = a.dtype == NQB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   bool ok = encode_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qw, a.K, a.N / 8, 128, 16, CU_TENSOR_MAP_SWIZZLE_64B);
   ok = ok && encode_2d(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.sc, G, a.N / 2, 1, 64, CU_TENSOR_MAP_SWIZZLE_NONE);
   ok = ok && encode_2d(&tz, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a.qz, G, a.N / 8, 1, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
   ok = ok && encode_2d(&tx, xdt, 2, a.x, a.M, a.K, (uint32_t)pl.TH, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   ok = ok && encode_2d(&to, xdt, 2, a.out, a.M, a.N, (uint32_t)pl.NT, kCols, CU_TENSOR_MAP_SWIZZLE_NONE);
+  // the fp32 slots as one matrix of [2 * clusters * kSlotRows][256]; without stream-K segments the map is never used
+  if (pl.fixup) ok = ok && encode_2d(&tsl, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, sp.slots, (uint64_t)2 * pl.nclusters * kSlotRows,
+                                     kCols * pl.ctas, 128, kCols, CU_TENSOR_MAP_SWIZZLE_NONE);
+  else tsl = to;
   if (!ok) return NQB200_ERR_LAUNCH;
-  return a.dtype == NQB200_BF16 ? launch_t<true>(tw, ts, tz, tx, to, sp, pl, a.stream)
-                                : launch_t<false>(tw, ts, tz, tx, to, sp, pl, a.stream);
+  return a.dtype == NQB200_BF16 ? launch_t<true>(tw, ts, tz, tx, to, tsl, sp, pl, a.stream)
+                                : launch_t<false>(tw, ts, tz, tx, to, tsl, sp, pl, a.stream);
 }
 
 }  // namespace nqb200

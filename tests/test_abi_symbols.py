@@ -68,6 +68,29 @@ def test_host_only_entry_points():
     assert lib.nqb200_gemm_allreduce_supported(4, 4096, 2048, 128, 0, 9, 1 << 20) == 0   # more ranks than the buffer layout holds
 
 
+def test_prefill_dispatch_is_a_host_side_decision():
+    """Which tcgen05 kernel a shape takes, how it is dealt and how much scratch it needs are decided on the
+    host: the benchmark sweep's points and the edges of the rule, without a GPU."""
+    lib = _lib.load()
+    name, launches, ws = lib.nqb200_gemm_kernel_name, lib.nqb200_gemm_launch_count, lib.nqb200_gemm_workspace_bytes
+    shapes = ((4096, 4096), (4096, 12288), (12288, 4096), (5120, 25600), (25600, 5120))
+    for K, N in shapes:
+        assert name(128, N, K, 128, 0) == b"prefill_tcgen05"           # up to 128 tokens: one CTA per tile
+        for M in (1024, 4096):
+            assert name(M, N, K, 128, 0) == b"prefill_tcgen05_pair", (M, K, N)
+    # whole tiles where the last wave costs less than stream-K's segments: one launch, scratch = counters only
+    assert launches(4096, 25600, 5120, 128, 0) == 1 and ws(4096, 25600, 5120, 128, 0) == ws(1024, 4096, 4096, 128, 0)
+    # few column tiles and a long K: stream-K, a second kernel and two fp32 segments of 256 x 256 per cluster
+    assert launches(4096, 5120, 25600, 128, 0) == 2
+    assert ws(4096, 5120, 25600, 128, 0) - ws(4096, 25600, 5120, 128, 0) == 2 * 74 * 256 * 256 * 4
+    # small layers stay with the single-CTA kernel however many tokens
+    assert name(256, 4096, 4096, 128, 0) == b"prefill_tcgen05"
+    assert name(192, 4096, 12288, 128, 1) == b"prefill_tcgen05"
+    # what the two-CTA kernel does not take: other group sizes, N not a multiple of 32
+    assert name(4096, 4096, 4096, 64, 0) != b"prefill_tcgen05_pair"
+    assert name(4096, 4112, 4096, 128, 0) != b"prefill_tcgen05_pair"
+
+
 def test_library_is_not_older_than_its_sources():
     from nanoquantization_b200.csrc import build
     assert not build._stale(), "libnqb200.so is older than csrc/: rebuild with python -m nanoquantization_b200.csrc.build"
