@@ -286,28 +286,35 @@ umma_prefill_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       tc_fence_after();
       const int tok0 = tile_t * kTileT;
       float* part = p.ksplit > 1 ? p.partials + (size_t)it.ks * p.M * p.N : nullptr;
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        const int n = tile_n * kTileN + nloc[blk];
+      // A lane holds, per token, two neighbouring columns: an even one in the first A block's accumulator and
+      // the odd one after it in the second's (nloc[1] == nloc[0] + 1), and the lanes of a warp hold 32 such
+      // pairs side by side: read both accumulators and store the pairs, 128 contiguous bytes per token and
+      // warp (256 for an fp32 partial) instead of 32 separate sectors.
+      {
+        const int n = tile_n * kTileN + nloc[0];
         const bool n_ok = n < p.N;
-        const float bv = (p.bias && n_ok && !part) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
-        for (int c0 = 16 * sub; c0 < p.nt; c0 += 16 * (kEpiWarps / 4)) {
-          uint32_t d[16];
-          tmem_ld_32x32b_x16(lane_base + kColD + 128 * blk + c0, d);
+        const float bv0 = (p.bias && n_ok && !part) ? bias_to_float(p.bias, p.bias_dtype, n) : 0.f;
+        const float bv1 = (p.bias && n_ok && !part) ? bias_to_float(p.bias, p.bias_dtype, n + 1) : 0.f;
+        for (int c0 = 8 * sub; c0 < p.nt; c0 += 8 * (kEpiWarps / 4)) {
+          uint32_t d0[8], d1[8];
+          tmem_ld_32x32b_x8(lane_base + kColD + c0, d0);
+          tmem_ld_32x32b_x8(lane_base + kColD + 128 + c0, d1);
           tc_wait_ld();
           if (!n_ok) continue;
           const int tok = tok0 + c0;
-          const int ntok = min(16, p.M - tok);  // <= 0 when the whole batch of columns is beyond M
+          const int ntok = min(8, p.M - tok);  // <= 0 when the whole batch of columns is beyond M
           if (part) {
             float* dst = part + (size_t)tok * p.N + n;
 #pragma unroll
-            for (int c = 0; c < 16; ++c)
-              if (c < ntok) __stcg(dst + (size_t)c * p.N, __uint_as_float(d[c]));
+            for (int c = 0; c < 8; ++c)
+              if (c < ntok) __stcg(reinterpret_cast<float2*>(dst + (size_t)c * p.N), make_float2(__uint_as_float(d0[c]), __uint_as_float(d1[c])));
           } else {
             uint16_t* dst = p.out + (size_t)tok * p.N + n;
 #pragma unroll
-            for (int c = 0; c < 16; ++c)
-              if (c < ntok) dst[(size_t)c * p.N] = float_to_raw16<BF16>(__uint_as_float(d[c]) + bv);
+            for (int c = 0; c < 8; ++c)
+              if (c < ntok)
+                *reinterpret_cast<uint32_t*>(dst + (size_t)c * p.N) =
+                    (uint32_t)float_to_raw16<BF16>(__uint_as_float(d0[c]) + bv0) | ((uint32_t)float_to_raw16<BF16>(__uint_as_float(d1[c]) + bv1) << 16);
           }
         }
       }
