@@ -44,6 +44,9 @@
 #include "tma_utils.cuh"
 #include "umma_utils.cuh"
 #include <mutex>
+#ifdef NQ_EXP_ENV
+#include <cstdlib>
+#endif
 
 #ifdef NQ_TL
 static unsigned long long* g_tl_host = nullptr;
@@ -84,7 +87,6 @@ constexpr uint32_t kWStageTx = 8192 + 256 + 64;
 constexpr int kColA = 0, kColD = 256, kTmemCols = 512;
 constexpr int kFixThreads = 256;
 constexpr int kSlotRows = 256;     // token rows of an fp32 slot (whatever the tile's token count), 256 columns each
-constexpr int kFixupUnits = 55;   // measured: 30 to 60 us, a unit being about 1 us
 
 struct Params {
   const void* bias; int bias_dtype; uint16_t* out;
@@ -584,7 +586,7 @@ __global__ void __launch_bounds__(kFixThreads) pair_fixup_kernel(const Params p,
 }
 
 // The shape of the work for a problem: CTAs per cluster, tokens per tile, clusters, units.
-struct Plan { int ctas, NT, TH, ntn, ntt, nclusters, quantum; long long U, t_units; bool fixup; size_t slot_floats; };
+struct Plan { int ctas, NT, TH, ntn, ntt, nclusters, quantum; long long U; double est_us; bool fixup; size_t slot_floats; };
 static Plan make_plan(int64_t M, int64_t N, int64_t K) {
   Plan pl;
   pl.ctas = 2;
@@ -596,13 +598,23 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K) {
   const int G = (int)(K / 128);
   pl.U = (long long)pl.ntn * pl.ntt * G;
   const long long maxc = kNumSMs / pl.ctas, items = (long long)pl.ntn * pl.ntt;
-  // Stream-K keeps every cluster busy to the end but sends the tiles that a range boundary cuts through fp32
-  // slots and a second kernel (about kFixupUnits units of time); dealing whole tiles needs neither and loses
-  // only the last wave's idle clusters.  Whichever ends first:
-  const long long t_stream = (pl.U + maxc - 1) / maxc + kFixupUnits, t_whole = (items + maxc - 1) / maxc * G;
+  // Stream-K keeps every cluster busy to the end, but the tiles that a range boundary cuts go through fp32 slots
+  // and a second kernel, and the clusters drift apart in k, so that the activations (which all column tiles of a
+  // token tile share) are fetched from L2 at scattered times: measured 0.95 us per unit + 10 us.  Whole tiles keep
+  // the clusters in step (0.78 us per unit in a full wave) and lose only the last wave's idle clusters, which
+  // itself runs faster the emptier it is (0.6 to 0.8 us per unit).  Fitted on M in 192..4096 x the sweep's five
+  // shapes, where it picks the faster dealing every time.  Whichever ends first:
+  const long long full = items / maxc, rem = items % maxc;
+  const double t_whole = G * (0.78 * (double)full + (rem ? 0.6 + 0.2 * (double)rem / (double)maxc : 0.0));
+  const double t_stream = 0.95 * (double)((pl.U + maxc - 1) / maxc) + 10.0;
+#ifdef NQ_EXP_ENV   // experiment builds only: force the dealing
+  bool whole = t_whole <= t_stream;
+  if (const char* e = getenv("NQB200_PAIR_MODE")) whole = e[0] == 'w';
+#else
   const bool whole = t_whole <= t_stream;
+#endif
   pl.quantum = whole ? G : 1;
-  pl.t_units = whole ? t_whole : t_stream;
+  pl.est_us = whole ? t_whole : t_stream;
   const long long parts = whole ? items : pl.U;
   pl.nclusters = (int)(parts < maxc ? parts : maxc);
   // some tile is shared between clusters unless every range boundary falls on a tile boundary
@@ -658,14 +670,17 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
 
 bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   if (!(M > 128 && g == 128 && K % 128 == 0 && N % 32 == 0)) return false;
+#ifdef NQ_EXP_ENV   // experiment builds only: force the choice of kernel
+  if (getenv("NQB200_NO_PAIR")) return false;
+  if (getenv("NQB200_PAIR_MODE")) return true;
+#endif
   // Against the single-CTA kernel (tiles of 256 columns x 128 tokens dealt to 148 CTAs with split-K, so hardly any
-  // imbalance): per unit of work this kernel is the faster by 15 %, but it deals 256 x 256 tiles to 74 pairs.
-  // It is used where its estimated time, imbalance or stream-K overhead included, stays below 1.3 x the
-  // balanced time + 15 units; over M in 192..4096 and the sweep's five shapes this rule was within 0.2 % of
-  // always picking the faster kernel.
+  // imbalance, about 1.1 us per unit): this kernel is used where its estimated time stays below that kernel's
+  // balanced time + 5 us.  Over M in 192..4096 and the sweep's five shapes this rule loses 0.01 % against always
+  // picking the faster of the two.
   const pair::Plan pl = pair::make_plan(M, N, K);
-  const long long balanced = ((N + 255) / 256) * ((M + 127) / 128) * (K / 128);   // x 1/148: units per SM
-  return 10 * 148 * pl.t_units <= 13 * balanced + 150 * 148;
+  const double balanced = (double)(((N + 255) / 256) * ((M + 127) / 128) * (K / 128)) / 148.0;   // units per SM
+  return pl.est_us <= 1.1 * balanced + 5.0;
 }
 
 int umma_pair_launches(int64_t M, int64_t N, int64_t K) { return pair::make_plan(M, N, K).fixup ? 2 : 1; }

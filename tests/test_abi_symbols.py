@@ -78,11 +78,12 @@ def test_prefill_dispatch_is_a_host_side_decision():
         assert name(128, N, K, 128, 0) == b"prefill_tcgen05"           # up to 128 tokens: one CTA per tile
         for M in (1024, 4096):
             assert name(M, N, K, 128, 0) == b"prefill_tcgen05_pair", (M, K, N)
-    # whole tiles where the last wave costs less than stream-K's segments: one launch, scratch = counters only
+    # whole tiles where the last wave costs less than stream-K: one launch, scratch = counters only
     assert launches(4096, 25600, 5120, 128, 0) == 1 and ws(4096, 25600, 5120, 128, 0) == ws(1024, 4096, 4096, 128, 0)
-    # few column tiles and a long K: stream-K, a second kernel and two fp32 segments of 256 x 256 per cluster
-    assert launches(4096, 5120, 25600, 128, 0) == 2
-    assert ws(4096, 5120, 25600, 128, 0) - ws(4096, 25600, 5120, 128, 0) == 2 * 74 * 256 * 256 * 4
+    assert launches(4096, 5120, 25600, 128, 0) == 1
+    # 80 tiles of a long K on 74 clusters: stream-K, a second kernel and two fp32 segments of 256 x 256 per cluster
+    assert launches(1024, 5120, 25600, 128, 0) == 2
+    assert ws(1024, 5120, 25600, 128, 0) - ws(4096, 25600, 5120, 128, 0) == 2 * 74 * 256 * 256 * 4
     # small layers stay with the single-CTA kernel however many tokens
     assert name(256, 4096, 4096, 128, 0) == b"prefill_tcgen05"
     assert name(192, 4096, 12288, 128, 1) == b"prefill_tcgen05"

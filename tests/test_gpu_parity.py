@@ -266,7 +266,7 @@ def test_gemm_sweep_every_point_vs_oracle(K, N, dtype, M):
     (1000, 1024, 25632, torch.float16, False, 1),
     (1000, 1024, 25632, torch.bfloat16, True, 1),
     (1100, 25600, 5152, torch.float16, True, 2),
-    (4096, 25600, 5120, torch.bfloat16, True, 2),
+    (2048, 25600, 5120, torch.bfloat16, True, 2),
     (700, 5120, 25600, torch.bfloat16, False, 1),
 ])
 def test_gemm_pair_kernel_ragged(M, K, N, dtype, bias, launches):
