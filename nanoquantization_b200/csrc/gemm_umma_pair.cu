@@ -44,14 +44,7 @@
 #include "tma_utils.cuh"
 #include "umma_utils.cuh"
 #include <mutex>
-#ifdef NQ_EXP_ENV
-#include <cstdlib>
-#endif
 
-#ifdef NQ_TL
-static unsigned long long* g_tl_host = nullptr;
-extern "C" int nqb200_debug_set_timeline(unsigned long long* p) { g_tl_host = p; return 0; }
-#endif
 namespace nqb200 {
 // One arrival on the barrier at this shared-memory offset in every CTA of `mask` (bit r: CTA r of the pair) when
 // every MMA issued so far by this thread has completed.  `bar` is the executing CTA's own address.
@@ -97,9 +90,6 @@ struct Params {
   uint32_t U;          // units: ntn * ntt * G
   float* slots; int slot_floats;  // [2 * nclusters][kSlotRows tokens][CTAs * 128 columns] fp32
   int* status;         // may be null
-#ifdef NQ_TL
-  unsigned long long* tl;
-#endif
 };
 
 // A wait suspends in hardware for up to kSuspendNs at a time (woken at once when the phase completes), so the
@@ -220,9 +210,6 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int tok_row = (item % p.ntt) * p.NT + (int)rank * p.TH;   // this CTA's part of the token tile
         const int s = i % kXStages;
         if (i >= kXStages && !wait_bar(&bar_done[s], ((i / kXStages) - 1) & 1, s_abort, status)) break;
-#ifdef NQ_TL
-        if (p.tl && blockIdx.x == 0 && i < 512) p.tl[i] = global_timer_ns();   // unit i - 4 has completed
-#endif
         const uint32_t st = smem_base + s * kXStageBytes, bar = smem_u32(&bar_xfull[s]);
         mbar_expect_tx(bar, tx_bytes);
         tma_load_2d(st, &tm_x, gk * kUnitK, tok_row, bar);
@@ -283,19 +270,11 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       };
       for (uint32_t u = u_begin; ok && u < u_end; ++u) {
         const bool last = gk == G - 1 || u == u_end - 1, more = u + 1 < u_end;
-#ifdef NQ_TL
-        const int ti = (int)(u - u_begin);
-        const bool tl_on = p.tl && blockIdx.x == 0 && ti < 256;
-        if (tl_on) p.tl[512 + 4 * ti] = (unsigned long long)clock64();
-#endif
         tc_fence_after();
         const uint32_t lo = desc_lo0 + s * (uint32_t)(kXStageBytes >> 4);
         const uint32_t a = tmem + kColA + s * 64;
         mma(lo, a, 0, first ? 0u : 1u);
         mma(lo, a, 1, 1u);
-#ifdef NQ_TL
-        if (tl_on) p.tl[512 + 4 * ti + 2] = (unsigned long long)clock64();
-#endif
         if (pending >= 0) { report(&bar_done[pending]); pending = -1; }
 #pragma unroll
         for (int ks = 2; ks < 6; ++ks) mma(lo, a, ks, 1u);
@@ -303,9 +282,6 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const bool ready = more && !last && mbar_test_wait(smem_u32(&bar_afull[sn]), phn);
         mma(lo, a, 6, 1u);
         mma(lo, a, 7, 1u);
-#ifdef NQ_TL
-        if (tl_on) p.tl[512 + 4 * ti + 3] = (unsigned long long)clock64();
-#endif
         if (last) {
           report(&bar_done[s]);
           report(&bar_dfull);
@@ -315,9 +291,6 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           pending = (int)s;
         }
         if (more && !ready && ok) ok = wait_bar(&bar_afull[sn], phn, s_abort, status);
-#ifdef NQ_TL
-        if (tl_on) p.tl[512 + 4 * ti + 1] = (unsigned long long)clock64() | ((unsigned long long)(ready ? 1 : 0) << 62);
-#endif
         first = last;
         if (++gk == G) gk = 0;
         s = sn; phase = phn;
@@ -607,12 +580,7 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K) {
   const long long full = items / maxc, rem = items % maxc;
   const double t_whole = G * (0.78 * (double)full + (rem ? 0.6 + 0.2 * (double)rem / (double)maxc : 0.0));
   const double t_stream = 0.95 * (double)((pl.U + maxc - 1) / maxc) + 10.0;
-#ifdef NQ_EXP_ENV   // experiment builds only: force the dealing
-  bool whole = t_whole <= t_stream;
-  if (const char* e = getenv("NQB200_PAIR_MODE")) whole = e[0] == 'w';
-#else
   const bool whole = t_whole <= t_stream;
-#endif
   pl.quantum = whole ? G : 1;
   pl.est_us = whole ? t_whole : t_stream;
   const long long parts = whole ? items : pl.U;
@@ -670,10 +638,6 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
 
 bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   if (!(M > 128 && g == 128 && K % 128 == 0 && N % 32 == 0)) return false;
-#ifdef NQ_EXP_ENV   // experiment builds only: force the choice of kernel
-  if (getenv("NQB200_NO_PAIR")) return false;
-  if (getenv("NQB200_PAIR_MODE")) return true;
-#endif
   // Against the single-CTA kernel (tiles of 256 columns x 128 tokens dealt to 148 CTAs with split-K, so hardly any
   // imbalance, about 1.1 us per unit): this kernel is used where its estimated time stays below that kernel's
   // balanced time + 5 us.  Over M in 192..4096 and the sweep's five shapes this rule loses 0.01 % against always
@@ -702,12 +666,6 @@ int launch_umma_pair(const GemmArgs& a) {
   sp.nclusters = pl.nclusters; sp.quantum = pl.quantum; sp.U = (uint32_t)pl.U;
   sp.status = (a.ws && a.ws_bytes >= (size_t)kCounterBytes) ? (int*)a.ws + (kCounterBytes / 4 - 1) : nullptr;
   sp.slots = nullptr; sp.slot_floats = (int)pl.slot_floats;
-#ifdef NQ_TL
-  sp.tl = g_tl_host;
-#endif
-#ifdef NQ_TL
-  sp.tl = g_tl_host;
-#endif
   if (pl.fixup) {
     if (!a.ws || a.ws_bytes < umma_pair_workspace_bytes(a.M, a.N, a.K)) return NQB200_ERR_WORKSPACE;
     if (!aligned16(a.ws)) return NQB200_ERR_MISALIGNED;
