@@ -263,6 +263,8 @@ def test_gemm_sweep_every_point_vs_oracle(K, N, dtype, M):
 # dispatch picks, so that a change of the rule cannot silently take these paths out of the test.
 @pytest.mark.parametrize("M,K,N,dtype,bias,launches", [
     (777, 4096, 12288, torch.float16, True, 1),
+    (192, 4096, 12288, torch.float16, True, 1),      # a single token tile of 192: MMA N = 192, 96 tokens per CTA
+    (130, 4096, 12288, torch.bfloat16, False, 1),    # 130 tokens in a tile of 160
     (1000, 1024, 25632, torch.float16, False, 1),
     (1000, 1024, 25632, torch.bfloat16, True, 1),
     (1100, 25600, 5152, torch.float16, True, 2),
@@ -289,7 +291,7 @@ def test_gemm_pair_kernel_ragged(M, K, N, dtype, bias, launches):
     y = m(x.to(DEV), out=buf[1:M + 1])
     torch.cuda.synchronize()
     assert bool((buf[0] == -7.25).all()) and bool((buf[M + 1] == -7.25).all())
-    rows = torch.cat([torch.tensor([0, 255, 256, M - 1]), torch.randperm(M, generator=g)[:28]])
+    rows = torch.cat([torch.tensor([0, min(255, M - 1), min(256, M - 1), M - 1]), torch.randperm(M, generator=g)[:28]])
     W = O.dequantize(qw, sc, qz)
     ref = x[rows].float() @ W.float()
     if b is not None:
