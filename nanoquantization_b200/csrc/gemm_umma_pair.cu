@@ -643,6 +643,7 @@ bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   // balanced time + 5 us.  Over M in 192..4096 and the sweep's five shapes this rule loses 0.01 % against always
   // picking the faster of the two.
   const pair::Plan pl = pair::make_plan(M, N, K);
+  if ((pl.U + 1) * pl.nclusters >= (1ll << 31)) return false;   // the kernel's 32-bit unit arithmetic
   const double balanced = (double)(((N + 255) / 256) * ((M + 127) / 128) * (K / 128)) / 148.0;   // units per SM
   return pl.est_us <= 1.1 * balanced + 5.0;
 }
