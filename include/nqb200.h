@@ -224,6 +224,16 @@ int nqb200_gemm_allreduce(const void* x, const void* qweight, const void* qscale
                           void* stream);
 int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int world, size_t slot_offset, void* out,
                           const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype, void* stream);
+/* The same sum for large messages (prefill-sized partial results: megabytes), in two shots: every rank
+ * adds its slice (1 / world of the message) of all ranks' partial results at `in_offset`, leaves the 16-bit
+ * sums in its slot at `result_offset`, and after a second barrier reads the other ranks' slices from their
+ * result slots: 2 (world - 1) / world of the message crosses NVLink per rank instead of world - 1 times
+ * it.  Same rules as nqb200_peer_allreduce; the result slots must alternate between two offsets from call
+ * to call (a peer may still be reading the previous one), the slot at `in_offset` may be the same every
+ * time.  No counterpart in the reference (single GPU). */
+int nqb200_peer_allreduce_large(void* const* peer_buffers, int rank, int world, size_t in_offset, size_t result_offset,
+                                void* out, const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype,
+                                void* stream);
 
 /* Waits for `stream`, then returns the status the kernels recorded in this
  * workspace: NQB200_OK, or NQB200_ERR_WAIT_TIMEOUT if a bounded device-side wait

@@ -58,6 +58,7 @@ SIGNATURES = {
     "nqb200_gemm_allreduce_supported": (_int, [_i64, _i64, _i64, _i64, _int, _int, _sz]),
     "nqb200_gemm_allreduce": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, ctypes.POINTER(_vp), _int, _int, _sz, _sz, _vp]),
     "nqb200_peer_allreduce": (_int, [ctypes.POINTER(_vp), _int, _int, _sz, _vp, _vp, _int, _i64, _i64, _int, _vp]),
+    "nqb200_peer_allreduce_large": (_int, [ctypes.POINTER(_vp), _int, _int, _sz, _sz, _vp, _vp, _int, _i64, _i64, _int, _vp]),
     "nqb200_workspace_status": (_int, [_vp, _sz, _vp]),
     "nqb200_gemm_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _i64, _int]),
     "nqb200_gemm_launch_count": (_int, [_i64, _i64, _i64, _i64, _int]),

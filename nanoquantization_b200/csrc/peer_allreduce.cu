@@ -104,6 +104,109 @@ __global__ void __launch_bounds__(kArThreadsLarge) peer_allreduce_kernel(const A
   }
 }
 
+// ---- two-shot all-reduce for large messages (the [tokens, hidden] partial sums of a row-parallel linear
+// in prefill: megabytes).  One-shot makes every rank read every rank's whole message (world x the bytes over
+// NVLink); here rank r adds slice r of all ranks' partials (reduce-scatter: (world - 1) / world of the message
+// read per rank), leaves the 16-bit sums in a second peer-visible slot, and after a second barrier every rank
+// reads the other ranks' slices from there (all-gather: the same amount again).  An element is added once, by
+// its owner, in rank order in fp32: every rank gets identical bits.  CTA b of a rank only ever exchanges with
+// CTA b of the others (the same partition of a slice over the CTAs on every rank), so the barriers are per
+// CTA, as in the one-shot kernel; they use two call numbers per launch.
+struct TsParams {
+  uint8_t* peers[kMaxRanks];
+  int rank, world;
+  size_t in_off, res_off;      // byte offsets inside the data region: partial sums (one slot), reduced slices
+  void* out;
+  const void* bias;
+  int bias_dtype;
+  int64_t n;                   // elements (multiple of 8)
+  int N;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(1024) peer_allreduce_twoshot_kernel(const TsParams p) {
+  grid_launch_dependents();
+  grid_dependency_wait();  // our partial sums were written by the kernel ahead on the stream
+  uint8_t* mine = p.peers[p.rank];
+  uint32_t* my_epoch = reinterpret_cast<uint32_t*>(mine + kArOffEpoch3) + blockIdx.x;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) { s_epoch = *my_epoch + 1; *my_epoch = s_epoch + 1; s_ok = 1; }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  // announce call number `v` to every rank and wait until every rank has announced it (or a later one)
+  auto barrier = [&](uint32_t v) {
+    __syncthreads();   // everything this CTA wrote is ordered before the announcement (release, cumulative)
+    if (threadIdx.x < p.world) {
+      uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peers[threadIdx.x] + kArOffFlags3) + blockIdx.x * kMaxRanks + p.rank;
+      st_flag(theirs, v);
+      const uint32_t* ours = reinterpret_cast<const uint32_t*>(mine + kArOffFlags3) + blockIdx.x * kMaxRanks + threadIdx.x;
+      const unsigned long long t0 = global_timer_ns(), limit = peer_wait_limit_ns(mine);
+      uint32_t it = 0;
+      while ((int32_t)(ld_flag(ours) - v) < 0) {
+        if ((++it & 255u) == 0 && global_timer_ns() - t0 > limit) {
+          atomicExch(reinterpret_cast<int*>(mine), NQB200_ERR_WAIT_TIMEOUT);
+          s_ok = 0;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    return s_ok != 0;
+  };
+  if (!barrier(e)) return;
+  const int64_t nvec = p.n >> 3, per = (nvec + p.world - 1) / p.world;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x, first = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  {
+    const int64_t lo = per * p.rank, hi = lo + per < nvec ? lo + per : nvec;
+    uint4* res = reinterpret_cast<uint4*>(mine + kArOffData + p.res_off);
+    for (int64_t i = lo + first; i < hi; i += step) {
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        v[r] = r < p.world ? ld_peer(reinterpret_cast<const uint4*>(p.peers[r] + kArOffData + p.in_off) + i) : make_uint4(0u, 0u, 0u, 0u);
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < p.world) {
+          const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += raw16_to_float<BF16>((uint16_t)(w[j] & 0xFFFF));
+            acc[2 * j + 1] += raw16_to_float<BF16>((uint16_t)(w[j] >> 16));
+          }
+        }
+      }
+      if (p.bias) {
+        const int n0 = (int)((i * 8) % p.N);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += bias_to_float(p.bias, p.bias_dtype, n0 + j);
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = (uint32_t)float_to_raw16<BF16>(acc[2 * j]) | ((uint32_t)float_to_raw16<BF16>(acc[2 * j + 1]) << 16);
+      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+      res[i] = ov;
+      reinterpret_cast<uint4*>(p.out)[i] = ov;
+    }
+  }
+  if (!barrier(e + 1)) return;
+  for (int q = 0; q < p.world; ++q) {
+    if (q == p.rank) continue;
+    const int64_t lo = per * q, hi = lo + per < nvec ? lo + per : nvec;
+    const uint4* src = reinterpret_cast<const uint4*>(p.peers[q] + kArOffData + p.res_off);
+    // four loads in flight per thread: NVLink's latency needs megabytes outstanding
+    int64_t i = lo + first;
+    for (; i + 3 * step < hi; i += 4 * step) {
+      const uint4 a = ld_peer(src + i), b = ld_peer(src + i + step), c = ld_peer(src + i + 2 * step), d = ld_peer(src + i + 3 * step);
+      uint4* o = reinterpret_cast<uint4*>(p.out);
+      o[i] = a; o[i + step] = b; o[i + 2 * step] = c; o[i + 3 * step] = d;
+    }
+    for (; i < hi; i += step) reinterpret_cast<uint4*>(p.out)[i] = ld_peer(src + i);
+  }
+}
+
 }  // namespace nqb200
 
 using namespace nqb200;
@@ -173,4 +276,23 @@ extern "C" int nqb200_peer_allreduce(void* const* peer_buffers, int rank, int wo
   const int threads = M * N * 2 >= (128 << 10) ? kArThreadsLarge : kArThreads;
   return launch_overlapped(dtype == NQB200_BF16 ? peer_allreduce_kernel<true> : peer_allreduce_kernel<false>, dim3(kArBlocks),
                            dim3(threads), 0, st, p);
+}
+
+extern "C" int nqb200_peer_allreduce_large(void* const* peer_buffers, int rank, int world, size_t in_offset, size_t result_offset,
+                                           void* out, const void* bias, int bias_dtype, int64_t M, int64_t N, int dtype,
+                                           void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return NQB200_ERR_BAD_SHAPE;
+  if (M < 0 || N <= 0 || (M * N) % 8 != 0 || in_offset % 16 != 0 || result_offset % 16 != 0) return NQB200_ERR_BAD_SHAPE;
+  if (dtype != NQB200_F16 && dtype != NQB200_BF16) return NQB200_ERR_BAD_DTYPE;
+  if (M == 0) return NQB200_OK;
+  if (!peer_buffers || !out) return NQB200_ERR_NULL_POINTER;
+  if (!aligned16(out)) return NQB200_ERR_MISALIGNED;
+  TsParams p;
+  for (int r = 0; r < kMaxRanks; ++r) p.peers[r] = r < world ? (uint8_t*)peer_buffers[r] : nullptr;
+  for (int r = 0; r < world; ++r) if (!p.peers[r]) return NQB200_ERR_NULL_POINTER;
+  p.rank = rank; p.world = world; p.in_off = in_offset; p.res_off = result_offset; p.out = out; p.bias = bias;
+  p.bias_dtype = bias_dtype; p.n = M * N; p.N = (int)N;
+  // always the same number of CTAs: each CTA has its own flags and call counter
+  return launch_overlapped(dtype == NQB200_BF16 ? peer_allreduce_twoshot_kernel<true> : peer_allreduce_twoshot_kernel<false>,
+                           dim3(kTsBlocks), dim3(1024), 0, (cudaStream_t)stream, p);
 }

@@ -7,6 +7,8 @@
 //   [512, 1536)       its flags: [CTA][source rank]
 //   [4096, 20480)     flags of the GEMM epilogue: [flag set][source rank], kEpilogueSets sets
 //   [20480, 22528)    call counters of the GEMM epilogue, one per flag set
+//   [22528, 23040)    call counters of the two-shot kernel, one per CTA (kTsBlocks)
+//   [23040, 27136)    its flags: [CTA][source rank]
 //   [32768, ...)      data slots
 #pragma once
 #include <stdint.h>
@@ -21,7 +23,10 @@ constexpr size_t kArOffWaitNs = 8;
 constexpr unsigned long long kArDefaultWaitNs = 1000000000ull;
 constexpr size_t kArOffEpoch = 256, kArOffFlags = 512;
 constexpr size_t kArOffFlags2 = 4096, kArOffEpoch2 = kArOffFlags2 + (size_t)kEpilogueSets * kMaxRanks * 4;
+constexpr int kTsBlocks = 128;
+constexpr size_t kArOffEpoch3 = kArOffEpoch2 + (size_t)kEpilogueSets * 4, kArOffFlags3 = kArOffEpoch3 + (size_t)kTsBlocks * 4;
 constexpr size_t kArOffData = 32768;
+static_assert(kArOffFlags3 + (size_t)kTsBlocks * kMaxRanks * 4 <= kArOffData, "header overlaps the data slots");
 static_assert(kArOffEpoch2 + (size_t)kEpilogueSets * 4 <= kArOffData, "header overlaps the data slots");
 
 // What a GEMM needs to all-reduce its output over peer memory in its own epilogue.

@@ -6,7 +6,9 @@ row-parallel linear writes its partial ``[M, N]`` result straight into a slot of
 for all ranks, adds the peers' slots in rank order and writes the sum to an ordinary tensor.
 For decode-sized inputs ``linear_all_reduce`` does both in the GEMM itself: the kernel that adds the
 GEMM's split-K partial sums stores the rank's result into every peer's slot and reduces over the
-ranks (``nqb200_gemm_allreduce``).  Messages larger than a slot go through NCCL.  The reference has no counterpart.
+ranks (``nqb200_gemm_allreduce``).  Messages larger than a slot take the two-shot kernel (``large_bytes``: the
+rank's partial result in one large slot, reduce-scatter and all-gather over peer memory in one launch) or, beyond
+that, NCCL.  The reference has no counterpart.
 """
 from __future__ import annotations
 
@@ -34,18 +36,20 @@ def _local(linear, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
 
 class PeerAllReduce:
     def __init__(self, group=None, slot_bytes: int = 1 << 20, num_slots: int = 8, fused: bool = True,
-                 max_message_bytes: int = 1 << 20, wait_limit_s: float = 1.0):
-        assert num_slots >= 3
+                 max_message_bytes: int = 1 << 20, wait_limit_s: float = 1.0, large_bytes: int = 0):
+        assert num_slots >= 3 and large_bytes % 256 == 0
         self.fused = fused  # reduce inside the GEMM's finishing kernel where the library supports it
         # larger messages go through NCCL (the one-shot kernel moves world x the message over NVLink per rank)
         self.max_message_bytes = max_message_bytes
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.slot_bytes, self.num_slots, self._next = slot_bytes, num_slots, 0
+        # behind the small slots: one slot for a large partial result and two, used alternately, for the reduced slices
+        self.large_bytes, self._large_base, self._large_next = large_bytes, slot_bytes * num_slots, 0
         lib = _lib.load()
         self.device = torch.device("cuda", torch.cuda.current_device())
         own = ctypes.c_void_p()
-        _lib.check(lib.nqb200_comm_alloc(ctypes.byref(own), slot_bytes * num_slots))
+        _lib.check(lib.nqb200_comm_alloc(ctypes.byref(own), slot_bytes * num_slots + 3 * large_bytes))
         self._own = own.value
         handle = ctypes.create_string_buffer(64)
         _lib.check(lib.nqb200_comm_export(self._own, handle))
@@ -63,7 +67,7 @@ class PeerAllReduce:
                 self._imported.append(p.value)
         _lib.check(lib.nqb200_comm_set_wait_limit(self._own, int(wait_limit_s * 1e9)))
         self._data_off = lib.nqb200_comm_data_offset()
-        self._bytes = torch.as_tensor(_DevicePtr(self._own + self._data_off, slot_bytes * num_slots), device=self.device)
+        self._bytes = torch.as_tensor(_DevicePtr(self._own + self._data_off, slot_bytes * num_slots + 3 * large_bytes), device=self.device)
         dist.barrier(group=group)
 
     def fits(self, M: int, N: int) -> bool:
@@ -99,6 +103,8 @@ class PeerAllReduce:
         if self.world == 1:
             return _local(linear, x)
         if not self.fits(M, N):
+            if self.fits_large(M, N):
+                return self.linear_all_reduce_large(linear, x)
             y = _local(linear, x)
             dist.all_reduce(y, group=self.group)
             return y
@@ -114,6 +120,23 @@ class PeerAllReduce:
         slot, off = self.next_slot(M, N, linear.qscales.dtype)
         _local(linear, x, slot)
         return self.reduce(off, M, N, linear.qscales.dtype)
+
+    def fits_large(self, M: int, N: int) -> bool:
+        return 0 < M * N * 2 <= self.large_bytes and (M * N) % 8 == 0
+
+    def linear_all_reduce_large(self, linear, x: torch.Tensor) -> torch.Tensor:
+        """``all_reduce(linear(x))`` for a prefill-sized result: the GEMM writes into the large slot, one
+        two-shot kernel per rank reduces over peer memory (``nqb200_peer_allreduce_large``)."""
+        M, N = x.shape[0], linear.out_features
+        dtype = linear.qscales.dtype
+        base = self._large_base
+        _local(linear, x, self._bytes[base:base + M * N * 2].view(dtype).view(M, N))
+        res = base + (1 + self._large_next) * self.large_bytes
+        self._large_next ^= 1
+        out = torch.empty(M, N, dtype=dtype, device=self.device)
+        _lib.check(_lib.load().nqb200_peer_allreduce_large(self._ptrs, self.rank, self.world, base, res, out.data_ptr(), None, 0,
+                                                           M, N, _lib.dtype_code(dtype), _lib.stream_ptr()))
+        return out
 
     def status(self) -> int:
         """0, or the code a bounded wait recorded when it gave up (waits for the current stream; the

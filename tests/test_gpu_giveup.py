@@ -104,3 +104,39 @@ def test_second_device_in_one_process():
                                               torch.cuda.current_stream().cuda_stream) == 0
         torch.cuda.synchronize()
     assert O.rel_err(out, O.w4a16_ref(c["x"], c["qweight"], c["qscales"], c["qzeros"])) <= 2e-3
+
+
+def test_two_shot_allreduce_one_rank_and_give_up():
+    """The large-message kernel: with one rank it copies the slot (both shots degenerate); with a second
+    rank that nobody plays its first barrier runs out, it records the time-out and writes nothing."""
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    M, N = 300, 512
+    nbytes = M * N * 2
+    big = 1 << 20
+    a, b = _alloc(lib, 3 * big), _alloc(lib, 3 * big)
+    try:
+        off = lib.nqb200_comm_data_offset()
+        data = torch.randn(M, N, generator=torch.Generator().manual_seed(2)).to(torch.float16).to(DEV)
+        _as_tensor(a + off, nbytes).view(torch.float16).view(M, N).copy_(data)
+        out = torch.full((M, N), -3.0, dtype=torch.float16, device=DEV)
+        one = (ctypes.c_void_p * 1)(a)
+        for k in range(3):   # result slots alternate
+            assert lib.nqb200_peer_allreduce_large(one, 0, 1, 0, (1 + k % 2) * big, out.data_ptr(), None, 0, M, N, _lib.F16, stream) == 0
+            assert lib.nqb200_comm_status(a, stream) == 0
+            assert torch.equal(out, data)
+        assert lib.nqb200_comm_set_wait_limit(a, 50_000_000) == 0
+        two = (ctypes.c_void_p * 2)(a, b)
+        out.fill_(-3.0)
+        assert lib.nqb200_peer_allreduce_large(two, 0, 2, 0, big, out.data_ptr(), None, 0, M, N, _lib.F16, stream) == 0
+        assert lib.nqb200_comm_status(a, stream) == TIMEOUT
+        assert bool((out == -3.0).all())
+        assert lib.nqb200_comm_status(a, stream) == 0
+        # bad arguments are statuses
+        assert lib.nqb200_peer_allreduce_large(two, 0, 2, 8, big, out.data_ptr(), None, 0, M, N, _lib.F16, stream) != 0
+        assert lib.nqb200_peer_allreduce_large(two, 2, 2, 0, big, out.data_ptr(), None, 0, M, N, _lib.F16, stream) != 0
+    finally:
+        torch.cuda.synchronize()
+        lib.nqb200_comm_free(a)
+        lib.nqb200_comm_free(b)

@@ -73,6 +73,27 @@ def _worker(rank, world, port, out):
         big = comm.linear_all_reduce(row.shard, torch.randn(600, 512, device=dev, dtype=torch.float16))  # too large: NCCL path
         assert big.shape == (600, 512)
         comm.close()
+        # prefill-sized results: the two-shot kernel (reduce-scatter + all-gather over peer memory in one launch)
+        # against NCCL's sum and the oracle; identical on every rank and from call to call (result slots alternate)
+        large = PeerAllReduce(slot_bytes=1 << 18, num_slots=4, large_bytes=4 << 20)
+        for Mb in (600, 2048):
+            cb = O.make_case(1024, 512, Mb, group_size=128, dtype=torch.float16, seed=21 + Mb)
+            xb = row.input_slice(cb["x"].to(dev)).contiguous()
+            row.load_full(cb["qweight"].to(dev), cb["qscales"].to(dev), cb["qzeros"].to(dev))
+            want = O.w4a16_ref(cb["x"], cb["qweight"], cb["qscales"], cb["qzeros"])
+            assert not large.fits(Mb, 512) and large.fits_large(Mb, 512) == ((Mb * 512) % 8 == 0)
+            if not large.fits_large(Mb, 512):
+                continue
+            ys = [large.linear_all_reduce(row.shard, xb) for _ in range(4)]
+            errs.append(O.rel_err(ys[-1], want))
+            ok = all(torch.equal(y_, ys[0]) for y_ in ys)
+            gathered = [torch.empty_like(ys[0]) for _ in range(world)]
+            dist.all_gather(gathered, ys[0])
+            ok = ok and all(torch.equal(g_, ys[0]) for g_ in gathered)
+            errs.append(0.0 if ok else 1.0)
+            errs.append(float((ys[0].float() - row(xb).float()).abs().max() / want.abs().max()))
+        errs.append(float(large.status()))
+        large.close()
         torch.cuda.synchronize()
         out.put((rank, errs))
     finally:
