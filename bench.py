@@ -218,7 +218,7 @@ def run_ours(args):
     comm = None
     if world > 1 and not args.nccl_only:
         from nanoquantization_b200.layers.peer_comm import PeerAllReduce
-        comm = PeerAllReduce(slot_bytes=2 << 20, num_slots=8, large_bytes=48 << 20)
+        comm = PeerAllReduce(slot_bytes=2 << 20, num_slots=8, large_bytes=48 << 20, wait_limit_s=10.0)
         for si in layers:
             for lin in layers[si]:
                 if hasattr(lin, "attach_comm"):
@@ -565,7 +565,7 @@ def serve_bench(world, rank, dev, dtype, requests=256, arch="qwen3-32b", max_bat
     comm = None
     if world > 1:
         from nanoquantization_b200.layers.peer_comm import PeerAllReduce
-        comm = PeerAllReduce(slot_bytes=2 << 20, num_slots=8, large_bytes=48 << 20)
+        comm = PeerAllReduce(slot_bytes=2 << 20, num_slots=8, large_bytes=48 << 20, wait_limit_s=10.0)
         model.attach_peer_comm(comm)
     g = torch.Generator().manual_seed(11)   # the same requests on every rank
     plen = torch.randint(128, 4097, (requests,), generator=g).tolist()
@@ -627,7 +627,7 @@ def decode_bench(world, rank, dev, dtype, batches=(1, 16, 64), context=2048, ste
     comm = None
     if world > 1:
         from nanoquantization_b200.layers.peer_comm import PeerAllReduce
-        comm = PeerAllReduce(slot_bytes=1 << 20, num_slots=8, large_bytes=48 << 20)   # 72 all-reduces per step: a multiple of the slot count
+        comm = PeerAllReduce(slot_bytes=1 << 20, num_slots=8, large_bytes=48 << 20, wait_limit_s=10.0)   # 72 all-reduces per step: a multiple of the slot count
     variants = [("nccl", None)] + ([("peer", comm)] if comm is not None else [])
     for (ar_name, ar_comm), B in [(v, b) for v in variants for b in batches]:
         model.attach_peer_comm(ar_comm)
