@@ -192,18 +192,21 @@ __global__ void __launch_bounds__(1024) peer_allreduce_twoshot_kernel(const TsPa
     }
   }
   if (!barrier(e + 1)) return;
-  for (int q = 0; q < p.world; ++q) {
-    if (q == p.rank) continue;
-    const int64_t lo = per * q, hi = lo + per < nvec ? lo + per : nvec;
-    const uint4* src = reinterpret_cast<const uint4*>(p.peers[q] + kArOffData + p.res_off);
-    // four loads in flight per thread: NVLink's latency needs megabytes outstanding
-    int64_t i = lo + first;
-    for (; i + 3 * step < hi; i += 4 * step) {
-      const uint4 a = ld_peer(src + i), b = ld_peer(src + i + step), c = ld_peer(src + i + 2 * step), d = ld_peer(src + i + 3 * step);
-      uint4* o = reinterpret_cast<uint4*>(p.out);
-      o[i] = a; o[i + step] = b; o[i + 2 * step] = c; o[i + 3 * step] = d;
+  // All-gather: the same positions of every other rank's slice at once, so that a thread has up to seven peer
+  // loads in flight (NVLink's latency needs megabytes outstanding); the last slice may be shorter.
+  for (int64_t i = first; i < per; i += step) {
+    uint4 v[kMaxRanks];
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) {
+      const int64_t j = per * q + i;
+      if (q < p.world && q != p.rank && j < nvec)
+        v[q] = ld_peer(reinterpret_cast<const uint4*>(p.peers[q] + kArOffData + p.res_off) + j);
     }
-    for (; i < hi; i += step) reinterpret_cast<uint4*>(p.out)[i] = ld_peer(src + i);
+#pragma unroll
+    for (int q = 0; q < kMaxRanks; ++q) {
+      const int64_t j = per * q + i;
+      if (q < p.world && q != p.rank && j < nvec) reinterpret_cast<uint4*>(p.out)[j] = v[q];
+    }
   }
 }
 
