@@ -56,8 +56,8 @@ namespace pair {
 
 constexpr int kCols = 128, kUnitK = 128;
 // Two rings of shared memory and one of tensor memory.  The packed weights of a unit (with scales and
-// zero-points: 8.5 KB) are done with as soon as the dequantisers have read them, so they get a deep ring of
-// their own and are fetched far ahead.  The unit's activations (up to 32 KB) must stay until its MMAs have
+// zero-points: 8.5 KB) are done with as soon as the dequantisers have read them, so they get a ring of
+// their own (three stages: what the 64 KB staging tile of the epilogue leaves).  The unit's activations (up to 32 KB) must stay until its MMAs have
 // completed, exactly as long as its slot of the A operand in tensor memory: those two rings have the same depth
 // and one completion report frees both.  A unit's data is therefore requested while four units of tensor-core
 // work are still queued, and the fetch of the weights, their dequantisation and the fetch of the activations
