@@ -403,9 +403,11 @@ def run_ours(args):
         dom = per_point[-1]["kernel"]
         roof_prefill = agg(lambda p: p["kernel"] == dom and p["M"] >= 1024, "tensor")
         dom_pts = [p for p in per_point if p["kernel"] == dom and p["M"] >= 1024]
-        # DRAM bytes per launch: an ncu capture of this kernel (profiles/) measured 1.011x its algorithmic read
-        # bytes (packed weights + activations; the output is still in L2 when the kernel ends)
-        roof_prefill["traffic"] = round(1.011 * sum(weight_bytes(p["K"], p["N"]) + 2 * p["M"] * p["K"] for p in dom_pts) / len(dom_pts))
+        # DRAM bytes per launch, from the ncu capture of this kernel at M = K = N = 4096 (profiles/): reads 1.19 x
+        # the algorithmic read bytes (packed weights + activations), writes 0.32 x the output (the rest is still
+        # in L2 when the kernel ends); scaled to the points of the sweep in proportion to those bytes
+        roof_prefill["traffic"] = round(sum(1.19 * (weight_bytes(p["K"], p["N"]) + 2 * p["M"] * p["K"]) + 0.32 * 2 * p["M"] * p["N"]
+                                            for p in dom_pts) / len(dom_pts))
         roof_prefill["traffic_unit"] = "bytes per launch (mean over the kernel's points)"
         roof_decode = agg(lambda p: p["M"] <= 16, "hbm")
         # ncu: both decode kernels read exactly their algorithmic bytes from DRAM (profiles/)
