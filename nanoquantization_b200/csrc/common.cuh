@@ -81,6 +81,7 @@ int stream_tile_columns();
 bool stream_silu_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 bool stream_allreduce_supported(int64_t M, int64_t N, int64_t K, int64_t g);
 int umma_prefill_launches(int64_t M, int64_t N, int64_t K);
+double umma_prefill_estimate_us(int64_t M, int64_t N, int64_t K);
 // gemm_umma_pair.cu: the two-SM (cta_group::2) tcgen05 kernel for more than 128 tokens.
 int launch_umma_pair(const GemmArgs& a);
 bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g);

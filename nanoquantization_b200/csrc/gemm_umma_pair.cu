@@ -638,14 +638,12 @@ static int launch_t(const CUtensorMap& tw, const CUtensorMap& ts, const CUtensor
 
 bool umma_pair_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
   if (!(M > 128 && g == 128 && K % 128 == 0 && N % 32 == 0)) return false;
-  // Against the single-CTA kernel (tiles of 256 columns x 128 tokens dealt to 148 CTAs with split-K, so hardly any
-  // imbalance, about 1.1 us per unit): this kernel is used where its estimated time stays below that kernel's
-  // balanced time + 5 us.  Over M in 192..4096 and the sweep's five shapes this rule loses 0.01 % against always
-  // picking the faster of the two.
+  // Against the single-CTA kernel: its own cost model's estimate for the shape, less the 10 us by which this
+  // kernel's fixed cost (cluster launch, tensor-memory allocation for a pair, a deeper pipeline to fill) exceeds
+  // that kernel's.  Over M in 192..4096 x the sweep's five shapes this rule picks the faster kernel every time.
   const pair::Plan pl = pair::make_plan(M, N, K);
   if ((pl.U + 1) * pl.nclusters >= (1ll << 31)) return false;   // the kernel's 32-bit unit arithmetic
-  const double balanced = (double)(((N + 255) / 256) * ((M + 127) / 128) * (K / 128)) / 148.0;   // units per SM
-  return pl.est_us <= 1.1 * balanced + 5.0;
+  return pl.est_us <= umma_prefill_estimate_us(M, N, K) - 10.0;
 }
 
 int umma_pair_launches(int64_t M, int64_t N, int64_t K) { return pair::make_plan(M, N, K).fixup ? 2 : 1; }

@@ -388,7 +388,7 @@ bool umma_prefill_supports(int64_t M, int64_t N, int64_t K, int64_t g) {
 
 // K is split across CTAs when whole tiles would fill the SMs badly (few tiles, or a last wave that
 // is mostly empty).  The split is the one a small cost model of the kernel predicts to be fastest.
-static int prefill_ksplit(int64_t M, int64_t N, int64_t K) {
+static int prefill_ksplit(int64_t M, int64_t N, int64_t K, double* est_us = nullptr) {
   const long long tiles = ((N + pre::kTileN - 1) / pre::kTileN) * ((M + pre::kTileT - 1) / pre::kTileT);
   const int G = (int)(K / 128);
   const int nt = M >= pre::kTileT ? pre::kTileT : (int)((M + 15) / 16) * 16;
@@ -405,7 +405,17 @@ static int prefill_ksplit(int64_t M, int64_t N, int64_t K) {
     if (ks == 1) unsplit_us = us;
     if (us < best_us - 1e-9) { best_us = us; best = ks; }
   }
-  return best_us < 0.92 * unsplit_us ? best : 1;  // the model is good to about 10 %
+  const bool split = best_us < 0.92 * unsplit_us;  // the model is good to about 10 %
+  if (est_us) *est_us = split ? best_us : unsplit_us;
+  return split ? best : 1;
+}
+
+// What the model above expects this kernel to take (without its fixed launch cost), for the choice between
+// this kernel and the two-SM one.
+double umma_prefill_estimate_us(int64_t M, int64_t N, int64_t K) {
+  double us = 0.0;
+  prefill_ksplit(M, N, K, &us);
+  return us;
 }
 
 int umma_prefill_launches(int64_t M, int64_t N, int64_t K) { return prefill_ksplit(M, N, K) > 1 ? 2 : 1; }
